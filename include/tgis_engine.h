@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define TGIS_ABI_VERSION 9
+#define TGIS_ABI_VERSION 10
 #define TGIS_MAX_REQUEST_ID 96
 #define TGIS_MAX_TOPN 12 /* reference forces max_logprobs >= 11: tgis_utils/args.py:214-216 */
 #define TGIS_MAX_STOP_TOKEN_IDS 8
@@ -70,6 +70,17 @@ typedef struct tgis_engine tgis_engine;
  *          token shift (TGIS_MIXER_WKV); dense GeGLU feed-forward.  The recurrent mixers keep fp32 state per sequence slot.
  *          bf16 or fp32 operands.  Single GPU, no LoRA slots. */
 #define TGIS_ARCH_FALERAX 3
+
+/*   REVEPEL: a layer list as well (tgis_engine_create_spec), fp32 residual stream.  A layer has ONE norm; its mixer and its
+ *          feed-forward both read that norm's output and are added to the stream together, each multiplied by a sigmoid
+ *          gate computed from the same normed row (TGIS_STYLE_PARALLEL_GATED); the mixer reads the normed row blended with
+ *          the previous token's (token shift; the previous normed row is part of the sequence slot's state).  Mixers:
+ *          sliding-window attention with sigmoid weights, rotary positions with YaRN scaling and optionally another
+ *          layer's keys and values (TGIS_MIXER_SIGMOID_ATTENTION), state-space duality scan (TGIS_MIXER_SSD), gated delta rule
+ *          with a decay per key channel (TGIS_MIXER_CHANNEL_DELTA); mixture-of-experts feed-forward with a sigmoid router,
+ *          squared-ReLU experts whose INPUT is weighted, and a shared expert (TGIS_MLP_MOE_SIGMOID).  Logits times
+ *          logit_scale.  bf16 or fp32 operands.  Single GPU, no LoRA slots. */
+#define TGIS_ARCH_REVEPEL 4
 
 /* Model + runtime configuration (bf16 decoder-only transformer; see TGIS_ARCH_*). */
 typedef struct tgis_config {
@@ -115,9 +126,14 @@ typedef struct tgis_config {
 #define TGIS_MIXER_PARALLEL 2        /* softcapped attention and a gated matrix memory on the same input, averaged */
 #define TGIS_MIXER_SELECTIVE_SCAN 3  /* short causal convolution + input-dependent state-space scan */
 #define TGIS_MIXER_WKV 4             /* token shift + per-channel decayed outer-product memory with a current-token bonus */
+#define TGIS_MIXER_SIGMOID_ATTENTION 5 /* grouped-query attention, rotary positions, window, weight = sigmoid(score + bias_h) */
+#define TGIS_MIXER_SSD 6             /* short convolution + per-head scalar-decay state-space scan, gated group norm */
+#define TGIS_MIXER_CHANNEL_DELTA 7   /* short convolutions + delta-rule memory whose key channels decay one by one */
 #define TGIS_MLP_NONE 0
 #define TGIS_MLP_MOE 1
 #define TGIS_MLP_DENSE_GELU 2        /* down(gelu_tanh(gate h) * (up h)), width `ff` */
+#define TGIS_MLP_MOE_SIGMOID 3       /* experts down(relu(up (s h))^2) weighted on their input by s = sigmoid(router logit), the
+                                      * `top` largest, their scores used as they are; shared expert of width shared_ff added (0: none) */
 typedef struct tgis_layer_spec {
   int32_t mixer;        /* TGIS_MIXER_* */
   int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank; /* per head: dim unrotated + rot_dim rotated query/key dims, vdim values */
@@ -143,10 +159,22 @@ typedef struct tgis_layer_spec {
   /* TGIS_MIXER_WKV: heads x dim (keys and values alike); rank of the decay's low-rank map */
   int32_t decay_rank;
   int32_t reserved;
+  /* TGIS_MIXER_SIGMOID_ATTENTION: heads / kv_heads / dim / vdim / window / rot_dims / rot_base / scale as above; rotary
+   * frequencies under YaRN scaling (yarn_factor <= 0: plain): f_i <- f_i / factor * r_i + f_i * (1 - r_i) with r_i the linear
+   * ramp between the dimensions that make yarn_fast and yarn_slow turns over yarn_original positions, cos and sin times
+   * 0.1 ln(factor) + 1.  kv_from > 0: no key / value projections, the layer reads the cache rows of layer kv_from - 1 (an
+   * earlier attention layer with projections of its own and the same kv_heads / dim / vdim / rotation) */
+  int32_t kv_from;
+  float yarn_factor, yarn_original, yarn_fast, yarn_slow;
+  /* TGIS_MIXER_SSD: heads x vdim channels, `state` entries per channel, `groups` B / C groups, `conv` taps, the gated output
+   * normed in norm_groups parts.  TGIS_MIXER_CHANNEL_DELTA: heads (values, vdim) / kv_heads (queries and keys, dim), `conv`
+   * taps, decay_rank and gate_rank: inner sizes of the two low-rank maps (decay logits, output gate) */
+  int32_t groups, norm_groups, gate_rank;
 } tgis_layer_spec;
 #define TGIS_STYLE_POST_NORM 1 /* x += rmsnorm(sublayer(x)) * w with a plain weight; unset: pre- and post-norm, weights stored
                                 * as deviations from one */
 #define TGIS_STYLE_TIED_HEAD 2 /* logits = embedding table x (no "head" tensor) */
+#define TGIS_STYLE_PARALLEL_GATED 4 /* one norm per layer; x += sigmoid(R1 n + b1) * mixer(shift(n)) + sigmoid(R2 n + b2) * ff(n) */
 #define TGIS_DTYPE_BF16 0 /* bf16 operands, fp32 accumulation; norms, softmax, routers and the residual sum in fp32 */
 #define TGIS_DTYPE_F32 1  /* everything in true fp32 (no TF32) */
 typedef struct tgis_model_spec {
@@ -157,6 +185,8 @@ typedef struct tgis_model_spec {
   float norm_eps;
   int32_t style;        /* TGIS_STYLE_* bits */
   const tgis_layer_spec* layers; /* [n_layers] */
+  float logit_scale;    /* logits = head x * logit_scale (0 is read as 1) */
+  int32_t reserved;
 } tgis_model_spec;
 
 /* What the adapter's proto->SamplingParams mapping (grpc_server.py:508-628) hands to the engine. */
@@ -266,6 +296,10 @@ int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec,
  * TGIS_MIXER_PARALLEL "l<i>.mix.left.q|k|v|g|o|q.norm|k.norm|out", "l<i>.mix.right.q|k|v|g|o|norm|i|i.b|f|f.b|out";
  * TGIS_MIXER_SELECTIVE_SCAN "l<i>.mix.in|conv|conv.b|x|dt|dt.b|A_log|D|o"; TGIS_MIXER_WKV "l<i>.mix.mu.r|mu.k|mu.v|mu.g|mu.w|
  * r|k|v|g|w1|w2|w0|u|norm|o". */
+/* cfg->arch == TGIS_ARCH_REVEPEL; parameter names: "embed", "head", "final.norm", "l<i>.norm1|shift|rg1|rg1.b|rg2|rg2.b",
+ * "l<i>.mlp.router|e<j>.up|e<j>.down|shared.up|shared.down"; TGIS_MIXER_SIGMOID_ATTENTION "l<i>.mix.q|k|v|pb|o" (k, v absent
+ * with kv_from); TGIS_MIXER_SSD "l<i>.mix.in|conv|conv.b|dt_bias|A_log|D|norm|o"; TGIS_MIXER_CHANNEL_DELTA "l<i>.mix.q|q.conv|k|
+ * k.conv|v|v.conv|b|A_log|norm|a1|a2|dt_bias|g1|g2|o". */
 /* name: HF Llama parameter name ("model.layers.3.self_attn.q_proj.weight", "lm_head.weight", ...) or
  * "tgis.rope_cos_sin" ([max_model_len,128] bf16 = cos|sin); arch OPT: HF OPT parameter names
  * ("model.decoder.layers.3.self_attn.q_proj.bias", "model.decoder.embed_positions.weight" with >= max_model_len + 2 rows,

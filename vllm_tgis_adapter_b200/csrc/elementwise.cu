@@ -796,6 +796,79 @@ cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_
   return launch_k(resid_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
 }
 
+// ---- layers whose mixer and feed-forward share one norm and are gated per channel (kernels.h: GatedTail) ----
+template <int VEC>
+__global__ void __launch_bounds__(NORM_THREADS) gated_tail_kernel(GatedTail a, int hidden, int T) {
+  extern __shared__ __align__(16) float row_buf[];
+  __shared__ float red[NORM_THREADS / 32];
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const size_t base = (size_t)t * hidden;
+  const float* gl = a.gl != nullptr ? a.gl + (size_t)t * a.ldg : nullptr;
+  const bool has_ff = a.y_rows != nullptr || a.y_side != nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+    const FV<VEC> ym = ld_fv<VEC>(a.y_mix + base + i), x = ld_fv<VEC>(a.resid + base + i);
+    FV<VEC> f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) f.v[e] = 0.f;
+    if (a.y_rows != nullptr)
+      for (int k = 0; k < a.top; ++k) {   // fixed k order
+        const FV<VEC> r = ld_fv<VEC>(a.y_rows + (size_t)a.inv[(size_t)t * a.top + k] * hidden + i);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) f.v[e] += r.v[e];
+      }
+    if (a.y_side != nullptr) {
+      const FV<VEC> r = ld_fv<VEC>(a.y_side + base + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) f.v[e] += r.v[e];
+    }
+    FV<VEC> r;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float g1 = gl != nullptr ? 1.f / (1.f + expf(-(gl[i + e] + a.b1[i + e]))) : 1.f;
+      float upd = g1 * ym.v[e];
+      if (has_ff) {
+        const float g2 = gl != nullptr ? 1.f / (1.f + expf(-(gl[hidden + i + e] + a.b2[i + e]))) : 1.f;
+        upd = fmaf(g2, f.v[e], upd);
+      }
+      r.v[e] = x.v[e] + upd;
+      ss = fmaf(r.v[e], r.v[e], ss);
+    }
+    st_fv<VEC>(a.resid + base + i, r);
+    st_fv<VEC>(row_buf + i, r);
+  }
+  // the token shift's state of this layer: the normed row its last token of the portion was given
+  if (a.prev_state != nullptr && (t + 1 == T || a.tok_slot[t + 1] != a.tok_slot[t])) {
+    float* dst = a.prev_state + (size_t)a.tok_slot[t] * hidden;
+    for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) st_fv<VEC>(dst + i, ld_fv<VEC>(a.n_cur + base + i));
+  }
+  const float rs = 1.f / sqrtf(block_sum<NORM_THREADS>(ss, red) / (float)hidden + a.eps);
+  for (int i = threadIdx.x * VEC; i < hidden; i += NORM_THREADS * VEC) {
+    const FV<VEC> r = ld_fv<VEC>(row_buf + i), w = ld_fv<VEC>(a.w_next + i);
+    FV<VEC> n;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) n.v[e] = r.v[e] * rs * w.v[e] * a.out_scale;
+    if (a.n_f32 != nullptr) st_fv<VEC>(a.n_f32 + base + i, n);
+    if (a.out != nullptr) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st_dt(a.out, a.out_dtype, base + i + e, n.v[e]);
+    }
+  }
+}
+cudaError_t gated_tail_launch(const GatedTail& a, int T, int hidden, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  if (a.y_mix == nullptr || a.resid == nullptr || a.w_next == nullptr || (size_t)hidden * 4 > 48 * 1024 ||
+      (a.gl != nullptr && (a.b1 == nullptr || a.b2 == nullptr)) || (a.prev_state != nullptr && (a.n_cur == nullptr || a.tok_slot == nullptr)))
+    return cudaErrorInvalidValue;
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = hidden % 4 == 0 && al16(a.y_mix) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_next) &&
+                   al16(a.n_f32) && al16(a.n_cur) && al16(a.prev_state);
+  if (vec) return launch_k(gated_tail_kernel<4>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden, T);
+  return launch_k(gated_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden, T);
+}
+
 __global__ void gather_rows_any_kernel(const int32_t* __restrict__ idx, const uint8_t* __restrict__ x,
                                        uint8_t* __restrict__ out, int row_bytes) {
   griddep_launch();

@@ -266,10 +266,21 @@ struct tgis_engine {
     float *mu = nullptr, *w0 = nullptr, *u = nullptr, *st_prev = nullptr;
     // TGIS_MLP_DENSE_GELU: gate / up rows interleaved, down
     void *w_gu = nullptr, *w_d = nullptr;
+    // ---- layers of the parallel gated style (TGIS_ARCH_REVEPEL): one norm, token shift, per-channel gates on both sublayers
+    void* w_gates = nullptr;          // [gates_cols, width]: mixer gate | feed-forward gate | router rows (operand type)
+    int gates_cols = 0;               // 2 width + experts, rounded up to a multiple of 8 (zero rows)
+    float *gate_b = nullptr, *shift = nullptr;   // [2 width] gate biases; [width] token-shift blend (st_prev: the previous normed row)
+    // TGIS_MIXER_SIGMOID_ATTENTION (w_in: q | k | v, or q alone when the layer reads another layer's cache rows)
+    SigAttnGeom sa{};
+    float* head_bias = nullptr;
+    int kv_src = -1;                  // layer whose k_cache / v_cache this layer reads (-1: its own)
+    // TGIS_MIXER_SSD (w_in as stored: z | x | B | C | dt) and TGIS_MIXER_CHANNEL_DELTA (w_in: q | k | v | beta | decay rank | gate rank)
+    int conv_ch = 0, c_b = 0, c_a1 = 0, c_g1 = 0;
+    void* w_g2 = nullptr;             // channel delta: output-gate up-projection (w_w2: the decay's)
   };
   std::vector<PnxLayer> pnx_layers;
   std::vector<void*> pnx_allocs;                     // everything pnx_alloc handed out
-  std::vector<std::pair<std::pair<float, int>, float*>> pnx_rope_tables;  // (base, dims) -> table
+  std::vector<std::pair<std::vector<float>, float*>> pnx_rope_tables;  // (base, dims, scaling) -> table
   std::set<std::string> pnx_loaded;
   size_t pnx_expected_tensors = 0;
   int pnx_dt = DT_BF16;                              // operand type of weights / matrix-product inputs / cache rows
@@ -278,6 +289,8 @@ struct tgis_engine {
   void *pnx_q = nullptr, *pnx_olat = nullptr;  // operand type: they feed the per-head products
   bool post_norm = false, tied_head = false;   // TGIS_STYLE_*
   float *flx_f1 = nullptr, *flx_f2 = nullptr, *flx_f3 = nullptr;   // fp32 scratch of the recurrent mixers
+  bool gated_style = false;                                        // TGIS_STYLE_PARALLEL_GATED
+  float* rvp_n[2] = {nullptr, nullptr};                            // fp32 normed rows of the current / the next layer
   void *flx_op2 = nullptr, *flx_mix = nullptr;                     // operand-type scratch: gated memory output, token-shift mixes
   float *pnx_final_norm = nullptr, *pnx_resid = nullptr, *pnx_y1 = nullptr, *pnx_gate = nullptr,
         *pnx_qabs = nullptr, *pnx_o = nullptr, *pnx_rl = nullptr, *pnx_mixw = nullptr, *pnx_sgate = nullptr,
@@ -485,7 +498,7 @@ struct tgis_engine {
     Fl = c.ffn / tp;
     Vl = c.vocab / tp;
     opt = c.arch == TGIS_ARCH_OPT;
-    pnx_on = c.arch == TGIS_ARCH_PONENEX || c.arch == TGIS_ARCH_FALERAX;  // the layer-list architectures
+    pnx_on = c.arch == TGIS_ARCH_PONENEX || c.arch == TGIS_ARCH_FALERAX || c.arch == TGIS_ARCH_REVEPEL;  // the layer-list architectures
     if (pnx_on) logits_bf16 = false;  // fp32 logits straight from the accumulators
     model_head_dim = opt ? c.head_dim : HEAD_DIM;
     attn_scale = 1.0f / std::sqrt((float)model_head_dim);  // zero-padded head dims add nothing to q . k
@@ -1168,21 +1181,38 @@ struct tgis_engine {
   void* pnx_alloc_dt(size_t count, bool zero = false) {
     return pnx_alloc<uint8_t>(count * dt_size(pnx_dt), zero);
   }
-  // cos | sin of p * base^(-2i / dims), i < dims / 2, evaluated in double and stored fp32: [max_model_len][dims]
-  const float* pnx_rope_table(float base, int dims) {
+  // cos | sin of p * f_i, f_i = base^(-2i / dims), i < dims / 2, evaluated in double and stored fp32: [max_model_len][dims].
+  // YaRN scaling (factor > 0): with dim(t) = dims ln(original / (2 pi t)) / (2 ln base) the dimension whose wave makes t turns
+  // over `original` positions, lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and the ramp
+  // r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):  f_i <- f_i / factor * r_i + f_i (1 - r_i), cos and sin times 0.1 ln(factor) + 1.
+  const float* pnx_rope_table(float base, int dims, float factor = 0.f, float original = 0.f, float fast = 0.f, float slow = 0.f) {
+    const std::vector<float> key = {base, (float)dims, factor, original, fast, slow};
     for (auto& kv : pnx_rope_tables)
-      if (kv.first.first == base && kv.first.second == dims) return kv.second;
+      if (kv.first == key) return kv.second;
     const int half = dims / 2;
+    std::vector<double> freq(std::max(half, 1));
+    double mag = 1.0;
+    for (int i = 0; i < half; ++i) freq[i] = std::pow((double)base, -2.0 * i / dims);
+    if (factor > 0.f) {
+      const double pi = 3.14159265358979323846;
+      auto turn_dim = [&](double turns) { return dims * std::log((double)original / (2.0 * pi * turns)) / (2.0 * std::log((double)base)); };
+      const double lo = std::max(std::floor(turn_dim(fast)), 0.0), hi = std::min(std::ceil(turn_dim(slow)), (double)dims - 1.0);
+      for (int i = 0; i < half; ++i) {
+        const double r = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+        freq[i] = freq[i] / (double)factor * r + freq[i] * (1.0 - r);
+      }
+      mag = 0.1 * std::log((double)factor) + 1.0;
+    }
     std::vector<float> tab((size_t)cfg.max_model_len * std::max(dims, 1));
     for (int pos = 0; pos < cfg.max_model_len; ++pos)
       for (int i = 0; i < half; ++i) {
-        const double a = (double)pos * std::pow((double)base, -2.0 * i / dims);
-        tab[(size_t)pos * dims + i] = (float)std::cos(a);
-        tab[(size_t)pos * dims + half + i] = (float)std::sin(a);
+        const double a = (double)pos * freq[i];
+        tab[(size_t)pos * dims + i] = (float)(std::cos(a) * mag);
+        tab[(size_t)pos * dims + half + i] = (float)(std::sin(a) * mag);
       }
     float* d = pnx_alloc<float>(tab.size());
     CK(cudaMemcpy(d, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice));
-    pnx_rope_tables.push_back({{base, dims}, d});
+    pnx_rope_tables.push_back({key, d});
     return d;
   }
 
@@ -1195,6 +1225,7 @@ struct tgis_engine {
     if (const char* e = getenv("TGIS_DUMP_RESID")) pnx_dump_path = e;
     post_norm = (pnx_spec.style & TGIS_STYLE_POST_NORM) != 0;
     tied_head = (pnx_spec.style & TGIS_STYLE_TIED_HEAD) != 0;
+    gated_style = (pnx_spec.style & TGIS_STYLE_PARALLEL_GATED) != 0;
     pnx_embed = pnx_alloc_dt(V * W);
     pnx_head = tied_head ? pnx_embed : pnx_alloc_dt(V * W);
     pnx_final_norm = pnx_alloc<float>(W);
@@ -1208,6 +1239,81 @@ struct tgis_engine {
       PnxLayer& l = pnx_layers[i];
       const tgis_layer_spec& s = pnx_layer_specs[i];
       l.sp = s;
+      if (gated_style) {
+        const size_t slots = S_max, E = s.mlp == TGIS_MLP_MOE_SIGMOID ? s.experts : 0;
+        l.norm1 = pnx_alloc<float>(W);
+        l.shift = pnx_alloc<float>(W);
+        l.gate_b = pnx_alloc<float>(2 * W, true);
+        l.gates_cols = (int)((2 * W + E + 7) / 8 * 8);
+        l.w_gates = pnx_alloc_dt((size_t)l.gates_cols * W, true);
+        l.st_prev = pnx_alloc<float>(slots * W, true);
+        pnx_expected_tensors += 4;  // norm1, shift, rg1, rg1.b
+        if (E > 0) {
+          const size_t ff = s.expert_ff, ffs = s.shared_ff;
+          l.w_gu_e = pnx_alloc_dt(E * ff * W);     // up-projections, one [ff, width] matrix per expert
+          l.w_d_e = pnx_alloc_dt(E * W * ff);
+          pnx_expected_tensors += 3 + 2 * E;  // rg2, rg2.b, router, e<j>.{up, down}
+          if (ffs > 0) {
+            l.w_gu_s = pnx_alloc_dt(ffs * W);
+            l.w_d_s = pnx_alloc_dt(W * ffs);
+            pnx_expected_tensors += 2;  // shared.{up, down}
+          }
+          m_top = std::max<size_t>(m_top, s.top); m_ff = std::max(m_ff, ff); m_ffs = std::max(m_ffs, ffs);
+        }
+        m_E = std::max<size_t>(m_E, l.gates_cols);
+        m_mix = std::max(m_mix, W);
+        if (s.mixer == TGIS_MIXER_SIGMOID_ATTENTION) {
+          const int H = s.heads, G = s.kv_heads;
+          l.sa = SigAttnGeom{H, G, s.dim, s.vdim, s.window, s.rot_dims, s.scale};
+          l.kv_src = s.kv_from > 0 ? s.kv_from - 1 : -1;
+          l.c_q = 0; l.c_k = H * s.dim; l.c_v = l.c_k + G * s.dim;
+          l.in_cols = ((l.kv_src >= 0 ? H * s.dim : l.c_v + G * s.vdim) + 7) / 8 * 8;
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_o = pnx_alloc_dt(W * H * s.vdim);
+          l.head_bias = pnx_alloc<float>(H);
+          l.cos_sin = s.rot_dims > 0 ? pnx_rope_table(s.rot_base, s.rot_dims, s.yarn_factor, s.yarn_original, s.yarn_fast, s.yarn_slow) : nullptr;
+          pnx_expected_tensors += l.kv_src >= 0 ? 3 : 5;  // q, pb, o (+ k, v)
+          m_q = std::max<size_t>(m_q, (size_t)H * s.dim);
+          m_ov = std::max<size_t>(m_ov, (size_t)H * s.vdim);
+          if (l.kv_src < 0) cache_row_bytes += (size_t)G * (s.dim + s.vdim) * dt_size(pnx_dt);
+          pnx_tile_tokens = std::min(pnx_tile_tokens, SIGATTN_TILE);
+        } else if (s.mixer == TGIS_MIXER_SSD) {
+          const size_t inner = (size_t)s.heads * s.vdim, GN = (size_t)s.groups * s.state;
+          l.conv_ch = (int)(inner + 2 * GN);
+          l.in_cols = (int)((2 * inner + 2 * GN + s.heads + 7) / 8 * 8);
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_o = pnx_alloc_dt(W * inner);
+          l.conv_w = pnx_alloc<float>((size_t)l.conv_ch * s.conv);
+          l.conv_b = pnx_alloc<float>(l.conv_ch);
+          l.dt_b = pnx_alloc<float>(s.heads);
+          l.A_log = pnx_alloc<float>(s.heads);
+          l.Dv = pnx_alloc<float>(s.heads);
+          l.mm_norm = pnx_alloc<float>(inner);
+          l.st_S = pnx_alloc<float>(slots * inner * s.state, true);
+          l.st_conv = pnx_alloc<float>(slots * std::max(s.conv - 1, 1) * l.conv_ch, true);
+          pnx_expected_tensors += 8;  // in, conv, conv.b, dt_bias, A_log, D, norm, o
+          m_f1 = std::max<size_t>(m_f1, l.conv_ch); m_f2 = std::max(m_f2, inner);
+        } else {  // TGIS_MIXER_CHANNEL_DELTA
+          const size_t H = s.heads, G = s.kv_heads, qk = G * s.dim, hv = H * s.vdim, hd = H * s.dim;
+          l.conv_ch = (int)(2 * qk + hv);
+          l.c_q = 0; l.c_k = (int)qk; l.c_v = (int)(2 * qk); l.c_b = l.conv_ch; l.c_a1 = l.c_b + (int)H; l.c_g1 = l.c_a1 + s.decay_rank;
+          l.in_cols = (l.c_g1 + s.gate_rank + 7) / 8 * 8;
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_w2 = pnx_alloc_dt(hd * s.decay_rank);
+          l.w_g2 = pnx_alloc_dt(hv * s.gate_rank);
+          l.w_o = pnx_alloc_dt(W * hv);
+          l.conv_w = pnx_alloc<float>((size_t)l.conv_ch * s.conv);
+          l.dt_b = pnx_alloc<float>(hd);
+          l.A_log = pnx_alloc<float>(H);
+          l.mm_norm = pnx_alloc<float>(hv);   // the per-head weight, repeated for every head
+          l.st_S = pnx_alloc<float>(slots * hd * s.vdim, true);
+          l.st_conv = pnx_alloc<float>(slots * std::max(s.conv - 1, 1) * l.conv_ch, true);
+          pnx_expected_tensors += 15;  // q, q.conv, k, k.conv, v, v.conv, b, A_log, norm, a1, a2, dt_bias, g1, g2, o
+          m_f1 = std::max<size_t>(m_f1, l.conv_ch); m_f2 = std::max(m_f2, hv); m_f3 = std::max(m_f3, hd + hv);
+        }
+        m_down = std::max<size_t>(m_down, l.in_cols);
+        continue;
+      }
       if (s.mlp == TGIS_MLP_DENSE_GELU) {
         l.norm2 = pnx_alloc<float>(W);
         l.w_gu = pnx_alloc_dt((size_t)2 * s.ff * W);
@@ -1344,8 +1450,12 @@ struct tgis_engine {
     flx_f1 = pnx_alloc<float>(T * m_f1);
     flx_f2 = pnx_alloc<float>(T * m_f2);
     flx_f3 = pnx_alloc<float>(T * m_f3);
-    flx_op2 = pnx_alloc_dt(T * m_f1, true);
+    flx_op2 = pnx_alloc_dt(T * std::max(m_f1, m_f2), true);
     flx_mix = pnx_alloc_dt(T * m_mix, true);
+    if (gated_style) {
+      rvp_n[0] = pnx_alloc<float>(T * W);
+      rvp_n[1] = pnx_alloc<float>(T * W);
+    }
     if (pnx_dt == DT_BF16) {
       pnx_attn_ws_floats = (size_t)8 << 20;  // 32 MB
       pnx_attn_ws = pnx_alloc<float>(pnx_attn_ws_floats);
@@ -1366,6 +1476,15 @@ struct tgis_engine {
       if (l.sp.mixer == TGIS_MIXER_PARALLEL) {
         l.k_cache = pnx_alloc_dt(nb * KV_BLOCK * l.ca.kv_heads * l.ca.dim, true);
         l.v_cache = pnx_alloc_dt(nb * KV_BLOCK * l.ca.kv_heads * l.ca.vdim, true);
+      }
+      if (l.sp.mixer == TGIS_MIXER_SIGMOID_ATTENTION) {
+        if (l.kv_src >= 0) {   // the rows another (earlier) layer writes
+          l.k_cache = pnx_layers[l.kv_src].k_cache;
+          l.v_cache = pnx_layers[l.kv_src].v_cache;
+        } else {
+          l.k_cache = pnx_alloc_dt(nb * KV_BLOCK * l.sa.kv_heads * l.sa.dim, true);
+          l.v_cache = pnx_alloc_dt(nb * KV_BLOCK * l.sa.kv_heads * l.sa.vdim, true);
+        }
       }
     }
     free_blocks.resize(num_blocks);
@@ -1412,6 +1531,75 @@ struct tgis_engine {
       if (sub == "mlp.down") return mat(l.w_d, W, s.ff);
     }
     auto in_rows = [&](int col, int64_t r) { return mat(at(l.w_in, (size_t)col * W), r, W); };
+    if (gated_style) {
+      const bool moe = s.mlp == TGIS_MLP_MOE_SIGMOID;
+      if (sub == "shift") return vec(l.shift, W);
+      if (sub == "rg1") return mat(l.w_gates, W, W);
+      if (sub == "rg1.b") return vec(l.gate_b, W);
+      if (sub == "rg2" || sub == "rg2.b") {
+        if (!moe) return rows * cols == (sub == "rg2" ? W * W : W) ? 0 : bad_shape();   // a gate with nothing to gate: not kept
+        return sub == "rg2" ? mat(at(l.w_gates, (size_t)W * W), W, W) : vec(l.gate_b + W, W);
+      }
+      if (moe) {
+        const int64_t E = s.experts, ff = s.expert_ff, ffs = s.shared_ff;
+        if (sub == "mlp.router") return mat(at(l.w_gates, (size_t)2 * W * W), E, W);
+        if (ffs > 0 && sub == "mlp.shared.up") return mat(l.w_gu_s, ffs, W);
+        if (ffs > 0 && sub == "mlp.shared.down") return mat(l.w_d_s, W, ffs);
+        if (sub.rfind("mlp.e", 0) == 0) {
+          const size_t d2 = sub.find('.', 5);
+          if (d2 == std::string::npos) return fail("unknown layer weight " + name);
+          const int ei = atoi(sub.substr(5, d2 - 5).c_str());
+          if (ei < 0 || ei >= E) return fail("expert index out of range in " + name);
+          const std::string which = sub.substr(d2 + 1);
+          if (which == "up") return mat(at(l.w_gu_e, (size_t)ei * ff * W), ff, W);
+          if (which == "down") return mat(at(l.w_d_e, (size_t)ei * W * ff), W, ff);
+        }
+      }
+      if (s.mixer == TGIS_MIXER_SIGMOID_ATTENTION) {
+        const int64_t H = s.heads, G = s.kv_heads;
+        if (sub == "mix.q") return in_rows(l.c_q, H * s.dim);
+        if (sub == "mix.k" && l.kv_src < 0) return in_rows(l.c_k, G * s.dim);
+        if (sub == "mix.v" && l.kv_src < 0) return in_rows(l.c_v, G * s.vdim);
+        if (sub == "mix.pb") return vec(l.head_bias, H);
+        if (sub == "mix.o") return mat(l.w_o, W, H * s.vdim);
+      } else if (s.mixer == TGIS_MIXER_SSD) {
+        const int64_t inner = (int64_t)s.heads * s.vdim, GN = (int64_t)s.groups * s.state;
+        if (sub == "mix.in") return mat(l.w_in, 2 * inner + 2 * GN + s.heads, W);
+        if (sub == "mix.conv") return place(l.conv_w, DT_F32, l.conv_ch, s.conv, s.conv, 1);
+        if (sub == "mix.conv.b") return vec(l.conv_b, l.conv_ch);
+        if (sub == "mix.dt_bias") return vec(l.dt_b, s.heads);
+        if (sub == "mix.A_log") return vec(l.A_log, s.heads);
+        if (sub == "mix.D") return vec(l.Dv, s.heads);
+        if (sub == "mix.norm") return vec(l.mm_norm, inner);
+        if (sub == "mix.o") return mat(l.w_o, W, inner);
+      } else {  // TGIS_MIXER_CHANNEL_DELTA
+        const int64_t H = s.heads, qk = (int64_t)s.kv_heads * s.dim, hv = H * s.vdim, hd = H * s.dim;
+        if (sub == "mix.q") return in_rows(l.c_q, qk);
+        if (sub == "mix.k") return in_rows(l.c_k, qk);
+        if (sub == "mix.v") return in_rows(l.c_v, hv);
+        if (sub == "mix.b") return in_rows(l.c_b, H);
+        if (sub == "mix.a1") return in_rows(l.c_a1, s.decay_rank);
+        if (sub == "mix.g1") return in_rows(l.c_g1, s.gate_rank);
+        if (sub == "mix.q.conv") return place(l.conv_w + (size_t)l.c_q * s.conv, DT_F32, qk, s.conv, s.conv, 1);
+        if (sub == "mix.k.conv") return place(l.conv_w + (size_t)l.c_k * s.conv, DT_F32, qk, s.conv, s.conv, 1);
+        if (sub == "mix.v.conv") return place(l.conv_w + (size_t)l.c_v * s.conv, DT_F32, hv, s.conv, s.conv, 1);
+        if (sub == "mix.a2") return mat(l.w_w2, hd, s.decay_rank);
+        if (sub == "mix.g2") return mat(l.w_g2, hv, s.gate_rank);
+        if (sub == "mix.dt_bias") return vec(l.dt_b, hd);
+        if (sub == "mix.A_log") return vec(l.A_log, H);
+        if (sub == "mix.o") return mat(l.w_o, W, hv);
+        if (sub == "mix.norm") {   // one weight of vdim entries for all heads: kept once per head
+          if (n != s.vdim) return bad_shape();
+          for (int h = 0; h < H; ++h)
+            if (weight_place_launch(tmp_src, s.vdim, 1, l.mm_norm + (size_t)h * s.vdim, DT_F32, 1, 1, 0) != cudaSuccess)
+              return fail("weight placement failed for " + name);
+          if (cudaDeviceSynchronize() != cudaSuccess) return fail("weight placement failed for " + name);
+          pnx_loaded.insert(name);
+          return 0;
+        }
+      }
+      return fail("unknown layer weight " + name);
+    }
     if (s.mixer == TGIS_MIXER_PARALLEL) {
       const int64_t H = s.heads, G = s.kv_heads, mH = s.mm_heads;
       if (sub == "mix.left.q") return in_rows(l.c_q, H * s.dim);
@@ -1665,6 +1853,118 @@ struct tgis_engine {
     pnx_dump_resid(T);
   }
 
+  // One layer of the parallel gated style (TGIS_STYLE_PARALLEL_GATED).  On entry rvp_n[li & 1] holds the layer's normed rows
+  // n = rmsnorm(x) * norm1 in fp32 and pnx_hA the same in the operand type; the mixer reads n blended with the previous
+  // token's n (token shift), the feed-forward, both gates and the router read n itself:
+  //   x += sigmoid(R1 n + b1) * mixer(shift(n)) + sigmoid(R2 n + b2) * ff(n)
+  // and the tail leaves the NEXT layer's normed rows (after the last layer: the final norm times the logit scale) behind.
+  void gated_layer(int li, int T, int S) {
+    PnxLayer& l = pnx_layers[li];
+    const tgis_layer_spec& s = l.sp;
+    const int W = cfg.hidden, A = pnx_dt;
+    const float eps = pnx_spec.norm_eps;
+    const int32_t* d_pos = ds<int32_t>(off_pos);
+    const int32_t* d_slot = ds<int32_t>(off_slotmap);
+    const int32_t* d_tokslot = ds<int32_t>(off_tokslot);
+    const AttnSeq* d_seqs = ds<AttnSeq>(off_seqs);
+    const bool last = li + 1 == (int)pnx_layers.size();
+    const bool moe = s.mlp == TGIS_MLP_MOE_SIGMOID;
+    float* n32 = rvp_n[li & 1];
+    const int gc = l.gates_cols;
+    // ---- what the mixer reads, and everything else that reads n: gate logits of both sublayers and the router logits
+    CK(token_shift_mix_launch(n32, W, l.shift, 1, d_pos, d_tokslot, l.st_prev, flx_mix, A, 0, T, stream));
+    ++n_launches;
+    pnx_gemm(pnx_hA, A, W, l.w_gates, pnx_rl, DT_F32, gc, T, gc, W);
+    const int ld = l.in_cols;
+    pnx_gemm(flx_mix, A, W, l.w_in, pnx_y1, DT_F32, ld, T, ld, W);
+    if (s.mixer == TGIS_MIXER_SIGMOID_ATTENTION) {
+      const int H = s.heads;
+      CK(sigattn_prep_launch(pnx_y1, ld, l.c_q, l.kv_src >= 0 ? -1 : l.c_k, l.c_v, l.sa, l.cos_sin, d_pos, d_slot, pnx_q, l.k_cache,
+                             l.v_cache, A, T, stream));
+      CK(sigattn_launch(pnx_q, l.k_cache, l.v_cache, A, d_seqs, ds<LatentTile>(off_ltiles), step_n_ltiles, ds<int32_t>(off_bt),
+                        bt_stride, l.head_bias, pnx_oA, A, l.sa, stream));
+      n_launches += 2;
+      pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
+    } else if (s.mixer == TGIS_MIXER_SSD) {
+      const int inner = s.heads * s.vdim, GN = s.groups * s.state, C = l.conv_ch;
+      CK(short_conv_silu_launch(pnx_y1 + inner, ld, C, l.conv_w, l.conv_b, s.conv, d_pos, d_tokslot, l.st_conv, flx_f1, nullptr, A, T, stream));
+      CK(conv_state_save_launch(pnx_y1 + inner, ld, C, s.conv, d_seqs, S, d_tokslot, l.st_conv, stream));
+      OuterScan os{};
+      os.mode = OUTER_SCAN_SSD;
+      os.v = flx_f1; os.k = flx_f1 + inner; os.q = flx_f1 + inner + GN; os.ldq = os.ldk = os.ldv = C;
+      os.q_scale = 1.f;
+      os.step_raw = pnx_y1 + 2 * inner + 2 * GN; os.lds = ld; os.step_b = l.dt_b; os.A_log = l.A_log; os.D = l.Dv;
+      os.S = l.st_S;
+      os.out = flx_f2; os.ldo = inner;
+      os.heads = s.heads; os.qk_heads = s.groups; os.dim = s.state; os.vdim = s.vdim;
+      CK(outer_scan_launch(os, d_seqs, S, d_tokslot, stream));
+      CK(head_norm_gate_launch(flx_f2, inner, s.norm_groups, inner / s.norm_groups, l.mm_norm, pnx_y1, ld, /*silu*/ 1, eps, flx_op2, A,
+                               T, stream, /*gate_first=*/1));
+      n_launches += s.conv > 1 ? 4 : 3;
+      pnx_gemm(flx_op2, A, inner, l.w_o, pnx_o, DT_F32, W, T, W, inner);
+    } else {  // TGIS_MIXER_CHANNEL_DELTA
+      const int H = s.heads, qk = s.kv_heads * s.dim, hv = H * s.vdim, hd = H * s.dim, C = l.conv_ch, ld3 = hd + hv;
+      CK(short_conv_silu_launch(pnx_y1, ld, C, l.conv_w, nullptr, s.conv, d_pos, d_tokslot, l.st_conv, flx_f1, nullptr, A, T, stream));
+      CK(conv_state_save_launch(pnx_y1, ld, C, s.conv, d_seqs, S, d_tokslot, l.st_conv, stream));
+      // the two low-rank maps: decay logits [heads x dim] and output-gate logits [heads x vdim], side by side in one buffer
+      pnx_gemm(pnx_y1 + l.c_a1, DT_F32, ld, l.w_w2, flx_f3, DT_F32, ld3, T, hd, s.decay_rank);
+      pnx_gemm(pnx_y1 + l.c_g1, DT_F32, ld, l.w_g2, flx_f3 + hd, DT_F32, ld3, T, hv, s.gate_rank);
+      DeltaScan dsn{};
+      dsn.q = flx_f1 + l.c_q; dsn.k = flx_f1 + l.c_k; dsn.v = flx_f1 + l.c_v; dsn.ldq = dsn.ldk = dsn.ldv = C;
+      dsn.decay_raw = flx_f3; dsn.ldd = ld3; dsn.decay_b = l.dt_b; dsn.A_log = l.A_log;
+      dsn.beta_raw = pnx_y1 + l.c_b; dsn.ldb = ld;
+      dsn.S = l.st_S;
+      dsn.out = flx_f2; dsn.ldo = hv;
+      dsn.heads = H; dsn.qk_heads = s.kv_heads; dsn.dim = s.dim; dsn.vdim = s.vdim;
+      (void)qk;
+      CK(delta_scan_launch(dsn, d_seqs, S, d_tokslot, stream));
+      CK(head_norm_gate_launch(flx_f2, hv, H, s.vdim, l.mm_norm, flx_f3 + hd, ld3, /*sigmoid*/ 0, eps, flx_op2, A, T, stream));
+      n_launches += s.conv > 1 ? 4 : 3;
+      pnx_gemm(flx_op2, A, hv, l.w_o, pnx_o, DT_F32, W, T, W, hv);
+    }
+    GatedTail gt{};
+    gt.y_mix = pnx_o;
+    gt.gl = pnx_rl; gt.ldg = gc; gt.b1 = l.gate_b; gt.b2 = l.gate_b + W;
+    if (moe) {
+      const int E = s.experts, top = s.top, ff = s.expert_ff, ffs = s.shared_ff;
+      CK(moe_route_launch(pnx_rl + 2 * W, gc, nullptr, E, top, pnx_ids, pnx_mixw, nullptr, T, stream, MOE_W_SIGMOID));
+      CK(moe_align_launch(pnx_ids, T, top, E, pnx_segoff, pnx_order, pnx_inv, stream));
+      n_launches += 2;
+      if (ffs > 0) {
+        pnx_gemm(pnx_hA, A, W, l.w_gu_s, pnx_actS, A, ffs, T, ffs, W, GEMM_ANY_RELU2);
+        pnx_gemm(pnx_actS, A, ffs, l.w_d_s, pnx_yS, DT_F32, W, T, W, ffs);
+        gt.y_side = pnx_yS;
+      }
+      {  // routed experts: one row segment per expert; the router's weight scales a row's INPUT, i.e. the sum before the activation
+        GemmAny a{};
+        a.X = pnx_hA; a.W = l.w_gu_e; a.Y = pnx_actE;
+        a.x_dtype = A; a.w_dtype = A; a.y_dtype = A;
+        a.T = T * top; a.N = ff; a.K = W; a.ldx = W; a.ldw = W; a.ldy = ff;
+        a.batch = 1; a.seg_off = pnx_segoff; a.n_groups = E; a.w_gs = (long long)ff * W;
+        a.gather = pnx_order; a.gather_div = top; a.mode = GEMM_ANY_RELU2; a.row_scale = pnx_mixw;
+        CK(gemm_any_launch(a, stream));
+        GemmAny b{};
+        b.X = pnx_actE; b.W = l.w_d_e; b.Y = pnx_yE;
+        b.x_dtype = A; b.w_dtype = A; b.y_dtype = DT_F32;
+        b.T = T * top; b.N = W; b.K = ff; b.ldx = ff; b.ldw = ff; b.ldy = W;
+        b.batch = 1; b.seg_off = pnx_segoff; b.n_groups = E; b.w_gs = (long long)W * ff;
+        CK(gemm_any_launch(b, stream));
+        n_launches += 2;
+      }
+      gt.y_rows = pnx_yE; gt.inv = pnx_inv; gt.top = top;
+    }
+    gt.resid = pnx_resid;
+    gt.w_next = last ? pnx_final_norm : pnx_layers[li + 1].norm1;
+    gt.eps = eps;
+    gt.out_scale = last && pnx_spec.logit_scale != 0.f ? pnx_spec.logit_scale : 1.f;
+    gt.n_f32 = last ? nullptr : rvp_n[(li + 1) & 1];
+    gt.out = pnx_hA; gt.out_dtype = A;
+    gt.n_cur = n32; gt.prev_state = l.st_prev; gt.tok_slot = d_tokslot;
+    CK(gated_tail_launch(gt, T, W, stream));
+    ++n_launches;
+    pnx_dump_resid(T);
+  }
+
   // embeddings + layer stack + final norm -> pnx_hA [T, hidden] (operand type), fp32 residual stream in pnx_resid
   void pnx_forward(int T, int S) {
     const int W = cfg.hidden, A = pnx_dt;
@@ -1676,6 +1976,13 @@ struct tgis_engine {
     const int32_t* d_bt = ds<int32_t>(off_bt);
     const LatentTile* d_tiles = ds<LatentTile>(off_ltiles);
     CK(embed_scale_f32_launch(d_tok, pnx_embed, A, pnx_spec.embed_scale, pnx_resid, T, W, cfg.vocab, stream));
+    if (gated_style) {
+      CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 0.f, rvp_n[0], DT_F32, W, T, W, eps, stream));
+      CK(convert_f32_launch(rvp_n[0], pnx_hA, A, (size_t)T * W, stream));
+      n_launches += 3;
+      for (int li = 0; li < (int)pnx_layers.size(); ++li) gated_layer(li, T, S);
+      return;
+    }
     if (post_norm) CK(convert_f32_launch(pnx_resid, pnx_hA, A, (size_t)T * W, stream));
     else CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 1.f, pnx_hA, A, W, T, W, eps, stream));
     n_launches += 2;
@@ -2779,7 +3086,8 @@ int tgis_abi_version(void) { return TGIS_ABI_VERSION; }
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
   if (!cfg || !out) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch == TGIS_ARCH_PONENEX || cfg->arch == TGIS_ARCH_FALERAX) return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
+  if (cfg->arch == TGIS_ARCH_PONENEX || cfg->arch == TGIS_ARCH_FALERAX || cfg->arch == TGIS_ARCH_REVEPEL)
+    return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
   if (cfg->arch != TGIS_ARCH_LLAMA && cfg->arch != TGIS_ARCH_OPT) return fail("unknown arch");
   if (cfg->arch == TGIS_ARCH_OPT) {
     if (cfg->head_dim != 64 && cfg->head_dim != HEAD_DIM) return fail("OPT: head_dim must be 64 or 128");
@@ -2825,7 +3133,8 @@ int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
 int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out) {
   if (!cfg || !spec || !out || !spec->layers) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch != TGIS_ARCH_PONENEX && cfg->arch != TGIS_ARCH_FALERAX) return fail("tgis_engine_create_spec: arch must be a layer-list architecture");
+  if (cfg->arch != TGIS_ARCH_PONENEX && cfg->arch != TGIS_ARCH_FALERAX && cfg->arch != TGIS_ARCH_REVEPEL)
+    return fail("tgis_engine_create_spec: arch must be a layer-list architecture");
   if (spec->n_layers < 1 || spec->n_layers > 4096) return fail("bad n_layers");
   if (spec->dtype != TGIS_DTYPE_BF16 && spec->dtype != TGIS_DTYPE_F32) return fail("dtype must be bf16 or fp32");
   if (cfg->hidden < 1 || cfg->hidden > 12288 || cfg->vocab < 1) return fail("bad hidden / vocab");
@@ -2836,6 +3145,39 @@ int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec,
     const tgis_layer_spec& s = spec->layers[i];
     const std::string at = " (layer " + std::to_string(i) + ")";
     const bool post = (spec->style & TGIS_STYLE_POST_NORM) != 0;
+    if ((spec->style & TGIS_STYLE_PARALLEL_GATED) != 0) {
+      if (post || (spec->style & TGIS_STYLE_TIED_HEAD) != 0) return fail("the parallel gated style has its own norm placement and an untied head");
+      if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_MOE_SIGMOID) return fail("unknown feed-forward kind" + at);
+      if (s.mlp == TGIS_MLP_MOE_SIGMOID && (s.experts < 1 || s.top < 1 || s.top > s.experts || s.top > 32 || s.expert_ff < 1 ||
+                                            s.shared_ff < 0 || s.experts > 2048))
+        return fail("bad mixture-of-experts sizes" + at);
+      if (s.mixer == TGIS_MIXER_SIGMOID_ATTENTION) {
+        if (s.heads < 1 || s.kv_heads < 1 || s.heads % s.kv_heads != 0 || s.dim < 1 || s.vdim < 1 || s.vdim > SIGATTN_MAX_VDIM ||
+            s.dim > 512)
+          return fail("bad attention sizes" + at);
+        if (s.rot_dims < 0 || s.rot_dims > s.dim || (s.rot_dims & 1)) return fail("rot.dims must be even and <= dim" + at);
+        if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail("bad rotary base" + at);
+        if (s.yarn_factor > 0.f && !(s.yarn_original > 0.f && s.yarn_fast > 0.f && s.yarn_slow > 0.f && s.rot_base > 1.f))
+          return fail("bad rotary scaling" + at);
+        if (s.kv_from > 0) {
+          if (s.kv_from - 1 >= i) return fail("kv_from must name an earlier layer" + at);
+          const tgis_layer_spec& o = spec->layers[s.kv_from - 1];
+          if (o.mixer != TGIS_MIXER_SIGMOID_ATTENTION || o.kv_from > 0 || o.kv_heads != s.kv_heads || o.dim != s.dim || o.vdim != s.vdim)
+            return fail("kv_from must name an attention layer with keys and values of its own and the same sizes" + at);
+        }
+      } else if (s.mixer == TGIS_MIXER_SSD) {
+        if (s.heads < 1 || s.vdim < 1 || s.state < 1 || s.state > OUTER_SCAN_MAX_DIM || s.groups < 1 || s.heads % s.groups != 0 ||
+            s.conv < 1 || s.conv > 64 || s.norm_groups < 1 || (s.heads * s.vdim) % s.norm_groups != 0)
+          return fail("bad state-space sizes" + at);
+      } else if (s.mixer == TGIS_MIXER_CHANNEL_DELTA) {
+        if (s.heads < 1 || s.kv_heads < 1 || s.heads % s.kv_heads != 0 || s.dim < 1 || s.dim > DELTA_SCAN_MAX_DIM || s.vdim < 1 ||
+            s.conv < 1 || s.conv > 64 || s.decay_rank < 1 || s.gate_rank < 1)
+          return fail("bad delta-rule sizes" + at);
+      } else {
+        return fail("unknown mixer type" + at);
+      }
+      continue;
+    }
     if (post != (s.mixer != TGIS_MIXER_LATENT_ATTENTION)) return fail("this mixer does not run in this norm style" + at);
     if (post) {
       if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_DENSE_GELU) return fail("unknown feed-forward kind" + at);

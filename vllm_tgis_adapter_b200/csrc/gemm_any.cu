@@ -5,7 +5,8 @@
 //   batched  blockIdx.z walks equal problems whose operands lie a fixed stride apart (one problem per attention head),
 //   grouped  the rows are cut into segments (seg_off, on the device) and segment g multiplies with weight matrix g
 //            (one segment per expert of a mixture-of-experts layer); rows of X may be gathered through an index list,
-// and five epilogues (plain store, SwiGLU or GeGLU over interleaved gate/up rows, per-(row, batch) scale, tanh).
+// and six epilogues (plain store, SwiGLU or GeGLU over interleaved gate/up rows, per-(row, batch) scale, tanh, squared ReLU of
+// the row-scaled sum).
 //
 // Every output element is the sum over k = 0 .. K-1 in ascending order inside one thread, so a row's result depends
 // neither on the other rows of the launch nor on where in a segment it landed.
@@ -42,6 +43,15 @@ __device__ __forceinline__ void st_from_float(__nv_bfloat16* p, float v) { *p = 
 __device__ __forceinline__ float glu_pair(int mode, float g, float u) {
   if (mode == GEMM_ANY_SWIGLU) return g / (1.f + expf(-g)) * u;
   return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+}
+
+// max(acc * s, 0)^2 with s the scale of the row's INPUT (GEMM_ANY_RELU2)
+__device__ __forceinline__ float relu2_scaled(float acc, float s) {
+  const float z = fmaxf(acc * s, 0.f);
+  return z * z;
+}
+__device__ __forceinline__ float relu2_row_scale(const GemmAny& a, int dst) {
+  return a.row_scale == nullptr ? 1.f : a.row_scale[a.gather != nullptr ? a.gather[dst] : dst];
 }
 
 template <class XT, class WT, class OT, int TM>
@@ -134,6 +144,11 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_kernel(GemmAny a) {
       for (int j = 0; j < 4; j += 2) {
         if (n + j + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + (n + j) / 2, glu_pair(a.mode, acc[i][j], acc[i][j + 1]));
       }
+    } else if (a.mode == GEMM_ANY_RELU2) {
+      const float s = relu2_row_scale(a, dst);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (n + j < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + j, relu2_scaled(acc[i][j], s));
     } else {
       const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z] : 1.f;
 #pragma unroll
@@ -279,7 +294,8 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
     for (int half = 0; half < 2; ++half) {
       const int dst = row_dst[wm * 16 * MI + mi * 16 + g + half * 8];
       if (dst < 0) continue;
-      const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z] : 1.f;
+      const float s = a.mode == GEMM_ANY_ROWSCALE ? a.row_scale[(size_t)dst * a.scale_ld + z]
+                      : a.mode == GEMM_ANY_RELU2  ? relu2_row_scale(a, dst) : 1.f;
 #pragma unroll
       for (int ni = 0; ni < 4; ++ni) {
         const int n = n0 + wn * 32 + ni * 8 + t2;
@@ -289,6 +305,9 @@ __global__ void __launch_bounds__(ANY_THREADS) gemm_any_mma_kernel(GemmAny a) {
         } else if (a.mode == GEMM_ANY_TANH) {
           if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, tanhf(v0));
           if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, tanhf(v1));
+        } else if (a.mode == GEMM_ANY_RELU2) {
+          if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, relu2_scaled(v0, s));
+          if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, relu2_scaled(v1, s));
         } else {
           if (n < a.N) st_from_float(Y + (size_t)dst * a.ldy + n, v0 * s);
           if (n + 1 < a.N) st_from_float(Y + (size_t)dst * a.ldy + n + 1, v1 * s);

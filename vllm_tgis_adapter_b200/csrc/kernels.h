@@ -241,6 +241,8 @@ constexpr int GEMM_ANY_SWIGLU = 1;    // W rows interleaved (gate_j, up_j): Y[ro
 constexpr int GEMM_ANY_ROWSCALE = 2;  // Y[row, n] = acc * row_scale[row * scale_ld + batch index]
 constexpr int GEMM_ANY_GEGLU = 3;     // as SWIGLU with the tanh form of gelu on the gate
 constexpr int GEMM_ANY_TANH = 4;      // Y[row, n] = tanh(acc)
+constexpr int GEMM_ANY_RELU2 = 5;     // Y[row, n] = max(acc * s, 0)^2, s = row_scale[gather ? gather[row] : row] (row_scale == nullptr: 1):
+                                      // a squared-ReLU layer whose INPUT row was multiplied by s
 struct GemmAny {
   const void* X; const void* W; void* Y;
   int x_dtype, w_dtype, y_dtype;   // DT_*
@@ -284,6 +286,22 @@ struct ResidTail {
   int cast_out;
 };
 cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream);
+// Tail of a layer whose mixer and feed-forward run side by side on ONE normed input and are gated per channel, row per CTA:
+//   resid[t] += sigmoid(gl[t, :hidden] + b1) * y_mix[t] + sigmoid(gl[t, hidden : 2 hidden] + b2) * (sum_k y_rows[inv[t * top + k]] + y_side[t])
+//   n = rmsnorm(resid[t]) * w_next * out_scale -> n_f32[t] (fp32, optional) and out[t] (operand type): the next layer's normed input
+//   (the feed-forward terms with null pointers drop out; gl == nullptr: both gates are one)
+// and, for the last row of every portion, prev_state[slot] = n_cur[t]: the token shift's state of THIS layer.
+struct GatedTail {
+  const float* y_mix;
+  const float* gl; int ldg; const float *b1, *b2;
+  const float* y_rows; const int32_t* inv; int top;
+  const float* y_side;
+  float* resid;
+  const float* w_next; float eps, out_scale;
+  float* n_f32; void* out; int out_dtype;
+  const float* n_cur; float* prev_state; const int32_t* tok_slot;
+};
+cudaError_t gated_tail_launch(const GatedTail& a, int T, int hidden, cudaStream_t stream);
 // rows of any DT_* matrix: out[r, :] = x[rows[r], :]
 cudaError_t gather_rows_any_launch(const void* x, const int32_t* rows, void* out, int R, int hidden, int dtype,
                                    cudaStream_t stream);
@@ -353,6 +371,27 @@ cudaError_t capattn_launch(const void* q, const void* k_cache, const void* v_cac
                            const float* gate, int gate_ld, void* out, int out_dtype, const CapAttnGeom& g,
                            cudaStream_t stream);
 
+// ---- attention_sigmoid.cu: grouped-query attention with rotary positions, a window, and sigmoid weights -------------------
+// weight(i, j) = sigmoid(scale * q_h(i) . k_g(j) + head_bias[h]) for 0 <= i - j < window (window <= 0: every earlier position),
+// o_h(i) = sum_j weight(i, j) v_g(j): nothing is normalised over the keys.  Query head h reads key/value head h / (heads / kv_heads).
+struct SigAttnGeom {
+  int heads, kv_heads, dim, vdim, window;
+  int rot_dims;      // the first rot_dims entries of every query / key head turn ("rotate half": i pairs with i + rot_dims / 2)
+  float scale;
+};
+constexpr int SIGATTN_TILE = 16;      // query tokens per CTA
+constexpr int SIGATTN_MAX_VDIM = 512; // value columns per head the FMA kernel's accumulators cover
+// y fp32 [T, ldy] holds q at column q_off (heads * dim), k at k_off (kv_heads * dim), v at v_off (kv_heads * vdim); k_off < 0:
+// the layer reads another layer's cache rows and only q is produced.  cos_sin fp32 [max_pos][rot_dims] = cos | sin (the
+// host folds any frequency scaling and magnitude in).  q_out DT_* [T, heads * dim]; cache rows as in attention_capped.cu.
+cudaError_t sigattn_prep_launch(const float* y, int ldy, int q_off, int k_off, int v_off, const SigAttnGeom& g,
+                                const float* cos_sin, const int32_t* positions, const int32_t* slot_mapping, void* q_out,
+                                void* k_cache, void* v_cache, int dtype, int T, cudaStream_t stream);
+// out DT_* [T, heads * vdim]; head_bias fp32 [heads] (nullptr: zeros)
+cudaError_t sigattn_launch(const void* q, const void* k_cache, const void* v_cache, int dtype, const AttnSeq* seqs,
+                           const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
+                           const float* head_bias, void* out, int out_dtype, const SigAttnGeom& g, cudaStream_t stream);
+
 // ---- recurrent.cu: mixers that carry a state from token to token ----------------------------------------------------
 // Every sequence owns one state slot per layer (the engine's sequence slot).  A kernel reads the slot's state for the first
 // token of a portion unless that token's position is 0 (then the state is zero: a slot needs no clearing when it is handed
@@ -387,7 +426,10 @@ cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_s
 //   OUTER_SCAN_DECAY:  o = (S + diag(u) k v^T)^T q;  S <- diag(w) S + k v^T,  w = exp(-exp(decay_raw + w0))
 //   OUTER_SCAN_GATED:  i = cap tanh((ig + b_i) / cap), f = logsigmoid(cap tanh((fg + b_f) / cap)), m' = max(f + m, i),
 //                      S <- e^(f + m - m') S + e^(i - m') k v^T, n likewise with k;  o = S^T q / (max(|n . q|, e^-m') + 1e-6)
-constexpr int OUTER_SCAN_DECAY = 0, OUTER_SCAN_GATED = 1;
+//   OUTER_SCAN_SSD:    dt = softplus(step_raw + step_b), S <- exp(-exp(A_log_h) dt) S + dt k v^T;  o = S^T q + D_h v
+//                      (one decay per head and token; the query reads the state after the token's update; q / k heads may be
+//                      shared by groups of heads: qk_heads)
+constexpr int OUTER_SCAN_DECAY = 0, OUTER_SCAN_GATED = 1, OUTER_SCAN_SSD = 2;
 constexpr int OUTER_SCAN_MAX_DIM = 256;
 struct OuterScan {
   int mode;
@@ -399,20 +441,46 @@ struct OuterScan {
   float* out; int ldo;   // fp32 [T, heads * vdim]
   int heads, dim, vdim;
   const float* x; float* x_last; int width;   // optional: x_last[slot] = x[last row of the portion] (the token shift's state)
+  int qk_heads;                                // q / k heads (head h reads h / (heads / qk_heads)); 0: one per head
+  const float* step_raw; int lds; const float *step_b, *A_log, *D;   // SSD: [T, heads], [heads], [heads], [heads]
 };
 cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
                               cudaStream_t stream);
 // out[t, h, :] = rmsnorm(o[t, h, :]) * w[h, :] * act(gate[t, h, :])    act: 0 sigmoid, 1 silu
+// gate_first != 0: out[t, h, :] = rmsnorm(o[t, h, :] * act(gate[t, h, :])) * w[h, :]   (the gate enters the norm)
 cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
-                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream);
+                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream,
+                                  int gate_first = 0);
+// The short convolution's state after a step: conv_state[slot][e][c] = input at position end - (taps - 1) + e, taken from the
+// step's rows x [T, ld] (channels c < n) or, for positions before the portion, from the old state.  Runs after the
+// convolution that read the old state.
+cudaError_t conv_state_save_launch(const float* x, int ld, int n, int taps, const AttnSeq* seqs, int n_seqs,
+                                   const int32_t* tok_slot, float* conv_state, cudaStream_t stream);
+// Gated delta rule with one decay per key channel, per head a matrix S [dim, vdim] (fp32):
+//   q <- q / sqrt(sum q^2 + 1e-6) * dim^-1/2,  k <- k / sqrt(sum k^2 + 1e-6)   (per q / k head; head h reads h / (heads / qk_heads))
+//   g = exp(-exp(A_log_h) * softplus(decay_raw + decay_b))   [dim];   beta = sigmoid(beta_raw)
+//   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+struct DeltaScan {
+  const float *q, *k, *v; int ldq, ldk, ldv;   // fp32 [T, qk_heads * dim] / [T, heads * vdim]
+  const float* decay_raw; int ldd; const float* decay_b; const float* A_log;   // [T, heads * dim], [heads * dim], [heads]
+  const float* beta_raw; int ldb;              // [T, heads]
+  float* S;                                    // [slots][heads][dim][vdim]
+  float* out; int ldo;                         // fp32 [T, heads * vdim]
+  int heads, qk_heads, dim, vdim;
+};
+constexpr int DELTA_SCAN_MAX_DIM = 256;
+cudaError_t delta_scan_launch(const DeltaScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                              cudaStream_t stream);
 // out[i] = x[i] in the operand type
 cudaError_t convert_f32_launch(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream);
 
 // ---- moe.cu: top-k router and the bookkeeping of the grouped expert products ----------------------------------------
 // logits fp32 [T, ld] (columns [0, E): experts; column E, when side_gate != nullptr: the shared expert's gate logit):
 //   ids[t, k], w[t, k] = the `top` largest of logits + bias and the softmax over just those;  side_gate[t] = sigmoid(.)
+// weight_mode MOE_W_SIGMOID: w[t, k] = sigmoid(logit) of each chosen expert, used as it is
+constexpr int MOE_W_SOFTMAX = 0, MOE_W_SIGMOID = 1;
 cudaError_t moe_route_launch(const float* logits, int ld, const float* bias, int E, int top, int32_t* ids, float* w,
-                             float* side_gate, int T, cudaStream_t stream);
+                             float* side_gate, int T, cudaStream_t stream, int weight_mode = MOE_W_SOFTMAX);
 // seg_off[E + 1]: rows per expert, prefix-summed; order[p] = t * top + k of the p-th row; inv[t * top + k] = p
 cudaError_t moe_align_launch(const int32_t* ids, int T, int top, int E, int32_t* seg_off, int32_t* order, int32_t* inv,
                              cudaStream_t stream);

@@ -2,7 +2,9 @@
 // one contiguous row segment per expert, which the grouped product of gemm_any.cu walks.  The expert products themselves
 // are matrix products (gemm_any.cu); the weighted sum of their outputs is part of the sublayer's tail (resid_tail_kernel).
 //
-// Router arithmetic is fp32 throughout: logits + bias, selection, and the softmax over the selected logits only.
+// Router arithmetic is fp32 throughout: logits + bias, selection, and the weights of the selected experts: the softmax over
+// the selected logits only (MOE_W_SOFTMAX) or each one's own sigmoid (MOE_W_SIGMOID; the order of sigmoid scores is the order
+// of the logits).
 #include <cfloat>
 
 #include "kernels.h"
@@ -17,7 +19,7 @@ constexpr int ROUTE_WARPS = 4;
 // one warp per token; dynamic shared memory: ROUTE_WARPS x E floats
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias, int E, int top,
-                 int32_t* __restrict__ ids, float* __restrict__ w, float* __restrict__ side_gate, int T) {
+                 int32_t* __restrict__ ids, float* __restrict__ w, float* __restrict__ side_gate, int T, int weight_mode) {
   extern __shared__ float sm[];
   griddep_launch();
   griddep_wait();
@@ -49,6 +51,10 @@ moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restri
       z[bi] = -FLT_MAX;
     }
     __syncwarp();
+  }
+  if (weight_mode == MOE_W_SIGMOID) {   // every chosen expert weighs its own sigmoid score; nothing is renormalised
+    if (lane < top) w[(size_t)t * top + lane] = 1.f / (1.f + expf(-my_val));
+    return;
   }
   // softmax over the selected logits (the first selected one is the largest)
   const float m = __shfl_sync(0xffffffffu, my_val, 0);
@@ -93,11 +99,11 @@ moe_align_kernel(const int32_t* __restrict__ ids, int n, int E, int32_t* __restr
 }  // namespace
 
 cudaError_t moe_route_launch(const float* logits, int ld, const float* bias, int E, int top, int32_t* ids, float* w,
-                             float* side_gate, int T, cudaStream_t stream) {
+                             float* side_gate, int T, cudaStream_t stream, int weight_mode) {
   if (T <= 0) return cudaSuccess;
   if (top < 1 || top > 32 || top > E || (size_t)ROUTE_WARPS * E * 4 > 48 * 1024) return cudaErrorInvalidValue;
   return launch_k(moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
-                  (size_t)ROUTE_WARPS * E * sizeof(float), stream, logits, ld, bias, E, top, ids, w, side_gate, T);
+                  (size_t)ROUTE_WARPS * E * sizeof(float), stream, logits, ld, bias, E, top, ids, w, side_gate, T, weight_mode);
 }
 
 cudaError_t moe_align_launch(const int32_t* ids, int T, int top, int E, int32_t* seg_off, int32_t* order, int32_t* inv,

@@ -66,7 +66,7 @@ short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const fl
   const int slot = tok_slot[t], p = positions[t];
   int nb = 0;  // predecessors of this token inside the batch (as far as the taps reach)
   while (nb < taps - 1 && t - nb - 1 >= 0 && tok_slot[t - nb - 1] == slot) ++nb;
-  float acc = b[c];
+  float acc = b != nullptr ? b[c] : 0.f;
   for (int j = taps - 1; j >= 0; --j) {   // oldest input first
     if (p - j < 0) continue;
     const float v = j <= nb ? xz[(size_t)(t - j) * ld + c]
@@ -212,6 +212,7 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   griddep_wait();
   const AttnSeq sq = seqs[blockIdx.x];
   const int h = blockIdx.y, tid = threadIdx.x, g = tid >> 5, lane = tid & 31;
+  const int hq = a.qk_heads > 0 ? h / (a.heads / a.qk_heads) : h;   // the q / k head this head reads
   const int c0 = blockIdx.z * OS_COLS, c = c0 + lane;
   const bool col_ok = c < a.vdim;
   const int slot = tok_slot[sq.q_start];
@@ -225,7 +226,11 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   }
   float u_r[RPT];   // DECAY: the bonus u of this thread's rows; GATED: the normaliser n of its rows (the same in every lane)
   float m_run = 0.f;
-  if (MODE == OUTER_SCAN_DECAY) {
+  const float ssd_rate = MODE == OUTER_SCAN_SSD ? -expf(a.A_log[h]) : 0.f, ssd_skip = MODE == OUTER_SCAN_SSD ? a.D[h] : 0.f;
+  if (MODE == OUTER_SCAN_SSD) {
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) u_r[j] = 0.f;
+  } else if (MODE == OUTER_SCAN_DECAY) {
 #pragma unroll
     for (int j = 0; j < RPT; ++j) {
       const int i = g + j * OS_GROUPS;
@@ -247,8 +252,8 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       const int tt = idx / D, i = idx % D;
       const size_t row = (size_t)(sq.q_start + t0 + tt);
       float* v3 = vec + (size_t)tt * 3 * D;
-      v3[i] = a.q[row * a.ldq + (size_t)h * D + i] * a.q_scale;
-      v3[D + i] = a.k[row * a.ldk + (size_t)h * D + i];
+      v3[i] = a.q[row * a.ldq + (size_t)hq * D + i] * a.q_scale;
+      v3[D + i] = a.k[row * a.ldk + (size_t)hq * D + i];
       if (MODE == OUTER_SCAN_DECAY)
         v3[2 * D + i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
     }
@@ -258,6 +263,11 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       const size_t row = (size_t)(sq.q_start + t0 + tid);
       gates[tid][0] = a.gate_cap * tanhf((a.ig[row * a.ldg + h] + a.ig_b[h]) / a.gate_cap);
       gates[tid][1] = logsigmoid_f(a.gate_cap * tanhf((a.fg[row * a.ldg + h] + a.fg_b[h]) / a.gate_cap));
+    }
+    if (MODE == OUTER_SCAN_SSD && tid < nt) {   // the token's step size and the decay it gives
+      const float dt = softplus_f(a.step_raw[(size_t)(sq.q_start + t0 + tid) * a.lds + h] + a.step_b[h]);
+      gates[tid][0] = expf(ssd_rate * dt);
+      gates[tid][1] = dt;
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
@@ -272,6 +282,16 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
             const float kv = v3[D + i] * vc;
             o = fmaf(v3[i], fmaf(u_r[j], kv, S[j]), o);
             S[j] = fmaf(v3[2 * D + i], S[j], kv);
+          }
+        }
+      } else if (MODE == OUTER_SCAN_SSD) {
+        const float da = gates[tt][0], dv = gates[tt][1] * vc;
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+          const int i = g + j * OS_GROUPS;
+          if (i < D) {
+            S[j] = fmaf(da, S[j], v3[D + i] * dv);
+            o = fmaf(v3[i], S[j], o);
           }
         }
       } else {
@@ -306,6 +326,7 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
         for (int r = 0; r < OS_GROUPS; ++r) d += part_n[tt][r];
         sum = sum / (fmaxf(fabsf(d), floor_m[tt]) + 1e-6f);
       }
+      if (MODE == OUTER_SCAN_SSD) sum = fmaf(ssd_skip, vcol[tt * OS_COLS + lane], sum);
       if (col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = sum;
     }
   }
@@ -336,18 +357,151 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   }
 }
 
+// ------------------------------------------------------------------------------------------------ convolution state
+// grid (sequences, ceil(n / 128)): one thread per channel moves the tail of its convolution forward
+__global__ void __launch_bounds__(128)
+conv_state_save_kernel(const float* __restrict__ x, int ld, int n, int taps, const AttnSeq* __restrict__ seqs,
+                       const int32_t* __restrict__ tok_slot, float* __restrict__ conv_state) {
+  griddep_launch();
+  griddep_wait();
+  const AttnSeq sq = seqs[blockIdx.x];
+  const int c = blockIdx.y * 128 + threadIdx.x;
+  if (c >= n) return;
+  const int K1 = taps - 1, first = sq.kv_len - sq.q_len, slot = tok_slot[sq.q_start];
+  float* cs = conv_state + (size_t)slot * K1 * n + c;
+  for (int e = 0; e < K1; ++e) {   // ascending: entry e + q_len is read before it could be rewritten
+    const int pp = sq.kv_len - K1 + e;
+    float v = 0.f;
+    if (pp >= first) v = x[(size_t)(sq.q_start + pp - first) * ld + c];
+    else if (pp >= 0) v = cs[(size_t)(e + sq.q_len) * n];
+    cs[(size_t)e * n] = v;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated delta rule
+// grid (sequences, heads, ceil(vdim / 32)); 256 threads = 32 value columns x DS_LPC lanes.  A column of S is independent of
+// the others (its write u_c needs only its own S[:, c] . k), so DS_LPC neighbouring lanes share one column, lane `sub` keeping
+// rows sub, sub + DS_LPC, ... in registers; the two sums over the rows that a token needs -- (g S)[:, c] . k for the write and
+// (g S)[:, c] . q for the read-out, which with the write becomes o_c = (g S)[:, c] . q + u_c (k . q) -- meet through one round of
+// shuffles.  Normalised q / k, the decays and the per-token scalars are staged in shared memory DS_CHUNK tokens at a time; the
+// token loop itself runs without a barrier.
+constexpr int DS_LPC = 8, DS_COLS = 32, DS_THREADS = DS_LPC * DS_COLS, DS_CHUNK = 16;
+template <int RPT>
+__global__ void __launch_bounds__(DS_THREADS)
+delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
+  extern __shared__ float ds_smem[];
+  const int D = a.dim;
+  float* vec = ds_smem;                                  // [DS_CHUNK][3][D]: q | k | decay
+  float* vcol = vec + (size_t)DS_CHUNK * 3 * D;          // [DS_CHUNK][DS_COLS]
+  __shared__ float beta_s[DS_CHUNK], kq_s[DS_CHUNK];
+  griddep_launch();
+  griddep_wait();
+  const AttnSeq sq = seqs[blockIdx.x];
+  const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane & (DS_LPC - 1);
+  const int hq = h / (a.heads / a.qk_heads);
+  const int cl = warp * (32 / DS_LPC) + lane / DS_LPC;   // column inside the CTA's 32
+  const int c = blockIdx.z * DS_COLS + cl;
+  const bool col_ok = c < a.vdim;
+  const int slot = tok_slot[sq.q_start];
+  const bool fresh = sq.kv_len - sq.q_len == 0;
+  float S[RPT];
+  float* Sg = a.S + (((size_t)slot * a.heads + h) * D) * a.vdim + (col_ok ? c : 0);
+#pragma unroll
+  for (int j = 0; j < RPT; ++j) {
+    const int i = sub + j * DS_LPC;
+    S[j] = (!fresh && col_ok && i < D) ? Sg[(size_t)i * a.vdim] : 0.f;
+  }
+  const float rate = -expf(a.A_log[h]), q_mult = 1.f / sqrtf((float)D);
+  for (int t0 = 0; t0 < sq.q_len; t0 += DS_CHUNK) {
+    const int nt = min(DS_CHUNK, sq.q_len - t0);
+    __syncthreads();   // the previous chunk's vectors are consumed
+    for (int idx = tid; idx < nt * D; idx += DS_THREADS) {
+      const int tt = idx / D, i = idx % D;
+      const size_t row = (size_t)(sq.q_start + t0 + tt);
+      float* v3 = vec + (size_t)tt * 3 * D;
+      v3[i] = a.q[row * a.ldq + (size_t)hq * D + i];
+      v3[D + i] = a.k[row * a.ldk + (size_t)hq * D + i];
+      v3[2 * D + i] = expf(rate * softplus_f(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.decay_b[(size_t)h * D + i]));
+    }
+    for (int idx = tid; idx < nt * DS_COLS; idx += DS_THREADS) {
+      const int tt = idx / DS_COLS, cc = idx % DS_COLS, col = blockIdx.z * DS_COLS + cc;
+      vcol[idx] = col < a.vdim ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + col] : 0.f;
+    }
+    if (tid < nt) beta_s[tid] = sigmoid_f(a.beta_raw[(size_t)(sq.q_start + t0 + tid) * a.ldb + h]);
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += DS_THREADS / 32) {   // unit vectors, and k . q of the unit vectors
+      float* v3 = vec + (size_t)tt * 3 * D;
+      float sq2 = 0.f, sk2 = 0.f, skq = 0.f;
+      for (int i = lane; i < D; i += 32) {
+        const float qv = v3[i], kv = v3[D + i];
+        sq2 = fmaf(qv, qv, sq2); sk2 = fmaf(kv, kv, sk2); skq = fmaf(qv, kv, skq);
+      }
+      sq2 = warp_sum_f(sq2); sk2 = warp_sum_f(sk2); skq = warp_sum_f(skq);
+      const float rq = q_mult / sqrtf(sq2 + 1e-6f), rk = 1.f / sqrtf(sk2 + 1e-6f);
+      for (int i = lane; i < D; i += 32) { v3[i] *= rq; v3[D + i] *= rk; }
+      if (lane == 0) kq_s[tt] = skq * rq * rk;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* v3 = vec + (size_t)tt * 3 * D;
+      float sk = 0.f, sqv = 0.f;
+#pragma unroll
+      for (int j = 0; j < RPT; ++j) {
+        const int i = sub + j * DS_LPC;
+        if (i < D) {
+          S[j] *= v3[2 * D + i];
+          sk = fmaf(S[j], v3[D + i], sk);
+          sqv = fmaf(S[j], v3[i], sqv);
+        }
+      }
+#pragma unroll
+      for (int o = DS_LPC / 2; o > 0; o >>= 1) {
+        sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        sqv += __shfl_xor_sync(0xffffffffu, sqv, o);
+      }
+      const float u = beta_s[tt] * (vcol[tt * DS_COLS + cl] - sk);
+#pragma unroll
+      for (int j = 0; j < RPT; ++j) {
+        const int i = sub + j * DS_LPC;
+        if (i < D) S[j] = fmaf(v3[D + i], u, S[j]);
+      }
+      if (sub == 0 && col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = fmaf(u, kq_s[tt], sqv);
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int j = 0; j < RPT; ++j) {
+      const int i = sub + j * DS_LPC;
+      if (i < D) Sg[(size_t)i * a.vdim] = S[j];
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ head norm + gate
 // grid (T, ceil(heads / 4)), 128 threads: one warp per (token, head)
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* __restrict__ o, int ldo, int heads, int vdim, const float* __restrict__ w,
                       const float* __restrict__ gate, int ldg, int act, float eps, void* __restrict__ out, int out_dtype,
-                      int out_ld) {
+                      int out_ld, int gate_first) {
   griddep_launch();
   griddep_wait();
   const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= heads) return;
   const float* orow = o + (size_t)t * ldo + (size_t)h * vdim;
   float ss = 0.f;
+  if (gate_first) {   // the gated values are what is normed
+    const float* grow = gate + (size_t)t * ldg + (size_t)h * vdim;
+    for (int i = lane; i < vdim; i += 32) {
+      const float v = orow[i] * (act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]));
+      ss = fmaf(v, v, ss);
+    }
+    const float rs = 1.f / sqrtf(warp_sum_f(ss) / (float)vdim + eps);
+    for (int i = lane; i < vdim; i += 32) {
+      const float v = orow[i] * (act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]));
+      st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, v * rs * w[(size_t)h * vdim + i]);
+    }
+    return;
+  }
   for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
   const float rs = 1.f / sqrtf(warp_sum_f(ss) / (float)vdim + eps);
   for (int i = lane; i < vdim; i += 32) {
@@ -423,15 +577,53 @@ cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seq
                               cudaStream_t stream) {
   if (n_seqs <= 0) return cudaSuccess;
   if (a.dim < 1 || a.dim > OUTER_SCAN_MAX_DIM || a.heads < 1 || a.heads > 65535 || a.vdim < 1) return cudaErrorInvalidValue;
+  if (a.qk_heads > 0 && a.heads % a.qk_heads != 0) return cudaErrorInvalidValue;
+  if (a.mode == OUTER_SCAN_SSD) {
+    if (a.step_raw == nullptr || a.step_b == nullptr || a.A_log == nullptr || a.D == nullptr) return cudaErrorInvalidValue;
+    return outer_scan_mode<OUTER_SCAN_SSD>(a, seqs, n_seqs, tok_slot, stream);
+  }
   return a.mode == OUTER_SCAN_GATED ? outer_scan_mode<OUTER_SCAN_GATED>(a, seqs, n_seqs, tok_slot, stream)
                                     : outer_scan_mode<OUTER_SCAN_DECAY>(a, seqs, n_seqs, tok_slot, stream);
 }
 
 cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
-                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream) {
+                                  int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream,
+                                  int gate_first) {
   if (T <= 0) return cudaSuccess;
   return launch_k(head_norm_gate_kernel, dim3(T, (heads + 3) / 4), dim3(128), 0, stream, o, ldo, heads, vdim, w, gate, ldg, act,
-                  eps, out, out_dtype, heads * vdim);
+                  eps, out, out_dtype, heads * vdim, gate_first);
+}
+
+cudaError_t conv_state_save_launch(const float* x, int ld, int n, int taps, const AttnSeq* seqs, int n_seqs,
+                                   const int32_t* tok_slot, float* conv_state, cudaStream_t stream) {
+  if (n_seqs <= 0 || taps <= 1) return cudaSuccess;
+  return launch_k(conv_state_save_kernel, dim3(n_seqs, (n + 127) / 128), dim3(128), 0, stream, x, ld, n, taps, seqs, tok_slot,
+                  conv_state);
+}
+
+template <int RPT>
+static cudaError_t delta_scan_rpt(const DeltaScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot, cudaStream_t stream) {
+  const dim3 grid(n_seqs, a.heads, (a.vdim + DS_COLS - 1) / DS_COLS);
+  const size_t smem = ((size_t)DS_CHUNK * 3 * a.dim + DS_CHUNK * DS_COLS) * sizeof(float);
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      const cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+  }
+  return launch_k(delta_scan_kernel<RPT>, grid, dim3(DS_THREADS), smem, stream, a, seqs, tok_slot);
+}
+cudaError_t delta_scan_launch(const DeltaScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
+                              cudaStream_t stream) {
+  if (n_seqs <= 0) return cudaSuccess;
+  if (a.dim < 1 || a.dim > DELTA_SCAN_MAX_DIM || a.heads < 1 || a.heads > 65535 || a.vdim < 1 || a.qk_heads < 1 ||
+      a.heads % a.qk_heads != 0)
+    return cudaErrorInvalidValue;
+  if (a.dim <= 8 * DS_LPC) return delta_scan_rpt<8>(a, seqs, n_seqs, tok_slot, stream);
+  if (a.dim <= 16 * DS_LPC) return delta_scan_rpt<16>(a, seqs, n_seqs, tok_slot, stream);
+  return delta_scan_rpt<32>(a, seqs, n_seqs, tok_slot, stream);
 }
 
 cudaError_t convert_f32_launch(const float* x, void* out, int out_dtype, size_t n, cudaStream_t stream) {

@@ -10,11 +10,12 @@ import ctypes as C
 import os
 from pathlib import Path
 
-ABI_VERSION = 9
-ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX, ARCH_FALERAX = 0, 1, 2, 3
+ABI_VERSION = 10
+ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX, ARCH_FALERAX, ARCH_REVEPEL = 0, 1, 2, 3, 4
 MIXER_LATENT_ATTENTION, MIXER_PARALLEL, MIXER_SELECTIVE_SCAN, MIXER_WKV = 1, 2, 3, 4
-MLP_NONE, MLP_MOE, MLP_DENSE_GELU = 0, 1, 2
-STYLE_POST_NORM, STYLE_TIED_HEAD = 1, 2
+MIXER_SIGMOID_ATTENTION, MIXER_SSD, MIXER_CHANNEL_DELTA = 5, 6, 7
+MLP_NONE, MLP_MOE, MLP_DENSE_GELU, MLP_MOE_SIGMOID = 0, 1, 2, 3
+STYLE_POST_NORM, STYLE_TIED_HEAD, STYLE_PARALLEL_GATED = 1, 2, 4
 DTYPE_BF16, DTYPE_F32 = 0, 1
 MAX_REQUEST_ID = 96
 MAX_TOPN = 12
@@ -46,6 +47,8 @@ class TgisLayerSpec(C.Structure):
         ("mm_heads", C.c_int32), ("mm_dim", C.c_int32), ("mm_vdim", C.c_int32), ("gate_cap", C.c_float),
         ("inner", C.c_int32), ("state", C.c_int32), ("dt_rank", C.c_int32), ("conv", C.c_int32),
         ("decay_rank", C.c_int32), ("reserved", C.c_int32),
+        ("kv_from", C.c_int32), ("yarn_factor", C.c_float), ("yarn_original", C.c_float), ("yarn_fast", C.c_float),
+        ("yarn_slow", C.c_float), ("groups", C.c_int32), ("norm_groups", C.c_int32), ("gate_rank", C.c_int32),
     ]
 
 
@@ -67,6 +70,7 @@ class TgisModelSpec(C.Structure):
     _fields_ = [
         ("n_layers", C.c_int32), ("dtype", C.c_int32), ("embed_scale", C.c_float), ("residual_mult", C.c_float),
         ("norm_eps", C.c_float), ("style", C.c_int32), ("layers", C.POINTER(TgisLayerSpec)),
+        ("logit_scale", C.c_float), ("reserved", C.c_int32),
     ]
 
 

@@ -30,15 +30,16 @@ class ModelConfig:
     rms_eps: float = 1e-5
     max_model_len: int = 2048
     arch: str = "llama"
-    # arch "ponenex" (engine/ponenex.py) and "falerax" (engine/falerax.py): the layers are described one by one;
+    # arch "ponenex" (engine/ponenex.py), "falerax" (engine/falerax.py) and "revepel" (engine/revepel.py): the layers are described one by one;
     # n_q_heads / n_kv_heads / ffn are unused
-    layers: list | None = None          # list[ponenex.LayerSpec] / list[falerax.LayerSpec]
+    layers: list | None = None          # list[ponenex.LayerSpec] / list[falerax.LayerSpec] / list[revepel.LayerSpec]
     embed_scale: float = 1.0
+    logit_scale: float = 1.0            # logits = head x * logit_scale
     residual_mult: float = 1.0
     dtype: str = "bfloat16"             # "bfloat16" | "float32" (layer-list architectures only)
 
 
-LAYER_LIST_ARCHS = ("ponenex", "falerax")   # created with tgis_engine_create_spec; bfloat16 or float32
+LAYER_LIST_ARCHS = ("ponenex", "falerax", "revepel")   # created with tgis_engine_create_spec; bfloat16 or float32
 
 
 # Named architectures (real dims; this offline build runs them on synthetic weights — SURVEY.md §0)
@@ -70,8 +71,11 @@ def cache_block_bytes(mc: ModelConfig) -> int:
     if mc.arch == "ponenex":
         esz = 4 if mc.dtype == "float32" else 2
         return KV_BLOCK_TOKENS * esz * sum(l.kv_rank + l.rot_dim for l in mc.layers)
-    if mc.arch == "falerax":
-        from .falerax import cache_row_elems
+    if mc.arch in ("falerax", "revepel"):
+        if mc.arch == "falerax":
+            from .falerax import cache_row_elems
+        else:
+            from .revepel import cache_row_elems
 
         return max(KV_BLOCK_TOKENS * (4 if mc.dtype == "float32" else 2) * cache_row_elems(mc), 1)
     return 2 * mc.n_layers * mc.n_kv_heads * KV_BLOCK_TOKENS * 128 * 2
@@ -159,7 +163,8 @@ class NativeEngine:
             cfg.shm_name = shm_name.encode()
         cfg.use_cuda_graphs, cfg.debug_gemm_ref, cfg.seed = int(use_cuda_graphs), 1 if debug_gemm_ref else 0, seed
         cfg.max_loras, cfg.max_lora_rank = int(max_loras), int(max_lora_rank) if max_loras else 0
-        archs = {"llama": _lib.ARCH_LLAMA, "opt": _lib.ARCH_OPT, "ponenex": _lib.ARCH_PONENEX, "falerax": _lib.ARCH_FALERAX}
+        archs = {"llama": _lib.ARCH_LLAMA, "opt": _lib.ARCH_OPT, "ponenex": _lib.ARCH_PONENEX, "falerax": _lib.ARCH_FALERAX,
+                 "revepel": _lib.ARCH_REVEPEL}
         if model.arch not in archs:
             raise EngineError(f"unknown architecture {model.arch!r}")
         cfg.arch = archs[model.arch]
@@ -168,8 +173,10 @@ class NativeEngine:
         if model.arch in LAYER_LIST_ARCHS:
             if model.arch == "ponenex":
                 from .ponenex import model_spec
-            else:
+            elif model.arch == "falerax":
                 from .falerax import model_spec
+            else:
+                from .revepel import model_spec
 
             spec, _keep = model_spec(model)   # _keep: the ctypes layer array the spec points into
             if self.lib.tgis_engine_create_spec(C.byref(cfg), C.byref(spec), C.byref(self._h)) != 0:

@@ -28,6 +28,10 @@ def model_config_from_hf(path: Path, max_model_len: int | None, dtype: str = "bf
         from .falerax import checkpoint_shapes, model_config_from_json
 
         return model_config_from_json(cfg, max_model_len, dtype, checkpoint_shapes(path))
+    if cfg.get("architecture") == "Revepel":
+        from .revepel import checkpoint_shapes, model_config_from_json
+
+        return model_config_from_json(cfg, max_model_len, dtype, checkpoint_shapes(path))
     archs = cfg.get("architectures") or []
     if cfg.get("model_type") == "opt" or any("OPT" in a for a in archs):
         return _opt_model_config(cfg, max_model_len)
@@ -98,8 +102,10 @@ def load_synthetic_weights(eng: NativeEngine, mc: ModelConfig, seed: int, device
     if mc.arch in LAYER_LIST_ARCHS:
         if mc.arch == "ponenex":
             from .ponenex import iter_synthetic_weights
-        else:
+        elif mc.arch == "falerax":
             from .falerax import iter_synthetic_weights
+        else:
+            from .revepel import iter_synthetic_weights
 
         for name, t in iter_synthetic_weights(mc, seed, f"cuda:{device}"):
             eng.load_weight(name, t)
@@ -184,8 +190,9 @@ def _resolve_model(args):
         return mc, path
     from .falerax import PRESETS as FALERAX_PRESETS
     from .ponenex import PRESETS as PONENEX_PRESETS
+    from .revepel import PRESETS as REVEPEL_PRESETS
 
-    PONENEX_PRESETS = {**PONENEX_PRESETS, **FALERAX_PRESETS}   # the presets of the layer-list architectures
+    PONENEX_PRESETS = {**PONENEX_PRESETS, **FALERAX_PRESETS, **REVEPEL_PRESETS}   # the presets of the layer-list architectures
     if args.model in PRESETS or args.model in PONENEX_PRESETS:
         if not args.synthetic_weights:
             raise ValueError(f"--model {args.model} is a preset name: pass --synthetic-weights or a model directory")
