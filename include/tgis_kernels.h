@@ -152,6 +152,23 @@ typedef struct tgis_k_capattn_geom {
 } tgis_k_capattn_geom;
 /* y fp32 [T, ldy] with q / k / v at the given columns -> normed, temperature-scaled queries (dt) [T, heads * dim] and the
  * cache rows K [blocks][32][kv_heads * dim], V [blocks][32][kv_heads * vdim] at slots[t] */
+/* csrc/attention_sigmoid.cu: rotary positions from a cos | sin table, window, weight = sigmoid(scale * q . k + head_bias[h]) */
+typedef struct tgis_k_sigattn_geom {
+  int32_t heads, kv_heads, dim, vdim, window, rot_dims;
+  float scale;
+} tgis_k_sigattn_geom;
+/* all pointers device memory; k_off < 0: only the queries are made (the layer reads another layer's cache rows) */
+int tgis_k_sigattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_sigattn_geom* g,
+                        const float* cos_sin, const int32_t* positions, const int32_t* slots, void* q_out, void* k_cache,
+                        void* v_cache, int32_t dt, int32_t T);
+int tgis_k_sigattn(const void* q, const void* k_cache, const void* v_cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                   const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, const float* head_bias, void* out,
+                   const tgis_k_sigattn_geom* g);
+/* csrc/recurrent.cu delta_scan_kernel (kernels.h DeltaScan); seqs_host as in tgis_k_attention, tok_slot device */
+int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* decay_raw,
+                      int32_t ldd, const float* decay_b, const float* A_log, const float* beta_raw, int32_t ldb, float* S,
+                      float* out, int32_t ldo, int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim,
+                      const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot);
 int tgis_k_capattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_capattn_geom* g,
                         const float* w_q, const float* w_k, float eps, const int32_t* positions, const int32_t* slots,
                         void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T);

@@ -642,6 +642,56 @@ int tgis_k_capattn(const void* q, const void* k_cache, const void* v_cache, int3
   return 0;
 }
 
+static SigAttnGeom to_sig(const tgis_k_sigattn_geom* g) {
+  return SigAttnGeom{g->heads, g->kv_heads, g->dim, g->vdim, g->window, g->rot_dims, g->scale};
+}
+
+int tgis_k_sigattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_sigattn_geom* g,
+                        const float* cos_sin, const int32_t* positions, const int32_t* slots, void* q_out, void* k_cache,
+                        void* v_cache, int32_t dt, int32_t T) {
+  KCK(sigattn_prep_launch(y, ldy, q_off, k_off, v_off, to_sig(g), cos_sin, positions, slots, q_out, k_cache, v_cache, dt, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_sigattn(const void* q, const void* k_cache, const void* v_cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
+                   const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, const float* head_bias, void* out,
+                   const tgis_k_sigattn_geom* g) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  std::vector<LatentTile> tiles;
+  for (int i = 0; i < n_seqs; ++i)
+    for (int q0 = 0; q0 < seqs[i].q_len; q0 += SIGATTN_TILE) tiles.push_back(LatentTile{i, q0, std::min(SIGATTN_TILE, seqs[i].q_len - q0), 0});
+  Tmp<AttnSeq> d_seqs;
+  Tmp<LatentTile> d_tiles;
+  Tmp<int32_t> d_bt;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  KCK(d_tiles.upload(tiles.data(), tiles.size()));
+  KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
+  KCK(sigattn_launch(q, k_cache, v_cache, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, head_bias, out, dt, to_sig(g), 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* decay_raw,
+                      int32_t ldd, const float* decay_b, const float* A_log, const float* beta_raw, int32_t ldb, float* S,
+                      float* out, int32_t ldo, int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim,
+                      const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  Tmp<AttnSeq> d_seqs;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  DeltaScan a{};
+  a.q = q; a.k = k; a.v = v; a.ldq = ldq; a.ldk = ldk; a.ldv = ldv;
+  a.decay_raw = decay_raw; a.ldd = ldd; a.decay_b = decay_b; a.A_log = A_log;
+  a.beta_raw = beta_raw; a.ldb = ldb;
+  a.S = S; a.out = out; a.ldo = ldo;
+  a.heads = heads; a.qk_heads = qk_heads; a.dim = dim; a.vdim = vdim;
+  KCK(delta_scan_launch(a, d_seqs.p, n_seqs, tok_slot, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
 int tgis_k_token_shift(const float* x, int32_t width, const float* mu, int32_t n_mix, const int32_t* positions,
                        const int32_t* tok_slot, const float* prev_state, void* out, int32_t out_dt, int64_t out_bs, int32_t T) {
   KCK(token_shift_mix_launch(x, width, mu, n_mix, positions, tok_slot, prev_state, out, out_dt, out_bs, T, 0));
