@@ -63,7 +63,7 @@ def parse_args():
     ap.add_argument("--sampling", default="greedy", choices=["greedy", "cfg3"],
                     help="cfg3 = repetition penalty 1.2 + length penalty (64, 1.05) + typical_p 0.9 sampling")
     ap.add_argument("--arch-compare", action="store_true",
-                    help="instead of the default workload: prefill / decode throughput of the Ponenex sizes beside Llama "
+                    help="instead of the default workload: prefill / decode throughput of the layer-list families' sizes beside Llama "
                          "stacks of equal hidden size, depth and active feed-forward width (--batch, --prompt-len, --gen-len)")
     ap.add_argument("--arch-sizes", default="", help="--arch-compare: only these presets (comma separated)")
     ap.add_argument("--layers", type=int, default=0, help="experiments: override the preset's layer count")
@@ -774,7 +774,7 @@ def run_ours(args) -> dict | None:
 # count and active feed-forward width, random weights, device-timed (the engine's CUDA events around every step).  Not the
 # default workload: `python bench.py --arch-compare` prints its own JSON line; the default JSON line is untouched.
 ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k"), ("falerax-1k", "llama-cmp-1k"),
-                ("falerax-2k", "llama-cmp-2k")]
+                ("falerax-2k", "llama-cmp-2k"), ("revepel-1k", "llama-cmp-1k"), ("revepel-2k", "llama-cmp-2k")]
 
 
 def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
@@ -813,6 +813,30 @@ def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
             # a decode step streams the weights once, every sequence's cache rows, and reads + writes its fp32 state
             bytes_ += 2.0 * (dense + 3 * h * l.ff) + B * (2.0 * ctx * cache + 8.0 * state)
         return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
+    if mc.arch == "revepel":
+        flops = bytes_ = 0.0
+        for l in mc.layers:
+            if l.kind == "attention":
+                own = l.kv_from is None
+                keys = min(ctx, l.window or ctx)
+                dense = h * (l.heads * l.dim + (l.kv_heads * (l.dim + l.vdim) if own else 0)) + l.heads * l.vdim * h
+                scan, state, cache = l.heads * keys * (l.dim + l.vdim), 0, l.kv_heads * (l.dim + l.vdim)
+            elif l.kind == "mamba2":
+                inner, gn = l.heads * l.vdim, l.groups * l.state
+                dense = h * (2 * inner + 2 * gn + l.heads) + inner * h
+                scan, state, cache, keys = 2 * inner * l.state, inner * l.state, 0, 0
+            else:
+                qk, hv, hd = l.kv_heads * l.dim, l.heads * l.vdim, l.heads * l.dim
+                dense = h * (2 * qk + hv + l.heads + l.decay_rank + l.gate_rank) + l.decay_rank * hd + l.gate_rank * hv + hv * h
+                scan, state, cache, keys = 3 * hd * l.vdim, hd * l.vdim, 0, 0
+            gates = h * (2 * h + l.experts) if l.experts else h * h
+            ff_tok = 2 * h * (l.top * l.expert_ff + l.shared_ff)
+            flops += 2.0 * (dense + gates + scan + ff_tok)
+            experts_touched = min(l.experts, B * l.top)
+            # a decode step streams the weights once (every expert the batch touches), every sequence's visible cache rows
+            # (a layer that shares another's rows reads them again), and reads + writes its fp32 state
+            bytes_ += 2.0 * (dense + gates + 2 * h * (experts_touched * l.expert_ff + l.shared_ff)) + B * (2.0 * keys * cache + 8.0 * state)
+        return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
     qd, kvd = mc.n_q_heads * 128, mc.n_kv_heads * 128
     per_layer = h * (qd + 2 * kvd) + qd * h + 3 * h * mc.ffn
     flops = mc.n_layers * 2.0 * (per_layer + mc.n_q_heads * ctx * 2 * 128) + 2.0 * h * v
@@ -830,7 +854,9 @@ def run_arch_compare(args) -> None:
     from vllm_tgis_adapter_b200.engine.falerax import PRESETS as FLX
     from vllm_tgis_adapter_b200.engine.ponenex import PRESETS as PNX
 
-    PNX = {**PNX, **FLX}   # the presets of the layer-list families
+    from vllm_tgis_adapter_b200.engine.revepel import PRESETS as RVP
+
+    PNX = {**PNX, **FLX, **RVP}   # the presets of the layer-list families
 
     torch.cuda.set_device(0)
     hbm_gbs, _ = peaks()
