@@ -337,7 +337,10 @@ def _alone():
         "attention": {"type": "attention", "mixer": _att(4, 2, 6, 10, 9, 4), "mlp": None},
         "attention_whole_head_rotates_no_scaling": {"type": "attention", "mixer": _att(3, 3, 8, 5, 40, 8, scaling=False), "mlp": None},
         "mamba2": {"type": "mamba2", "mixer": {"heads": 6, "vdim": 4, "state": 5, "groups": 2, "norm_groups": 3, "conv": 3}, "mlp": None},
+        "mamba2_one_wide_norm_group": {"type": "mamba2", "mixer": {"heads": 16, "vdim": 66, "state": 8, "groups": 4, "norm_groups": 1, "conv": 2},
+                                       "mlp": None},
         "channel_delta": {"type": "channel_delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 6, "vdim": 5, "conv": 3}, "mlp": None},
+        "channel_delta_keys_of_33": {"type": "channel_delta", "mixer": {"heads": 2, "kv_heads": 1, "dim": 33, "vdim": 35, "conv": 2}, "mlp": None},
         "experts": {"type": "attention", "mixer": _att(1, 1, 2, 2, 1, 0), "mlp": _moe(6, 2, 10, 14)},
     }
 

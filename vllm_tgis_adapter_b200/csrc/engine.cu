@@ -1732,6 +1732,7 @@ struct tgis_engine {
     if (pnx_tc && x_tma_ok && pnx_dt == DT_BF16 && x_dt == DT_BF16 && ldx == K && K % 64 == 0 && K >= 256 && N % 8 == 0 &&
         N >= 128 && !cfg.debug_gemm_ref && (reinterpret_cast<uintptr_t>(Y) & 15) == 0 && (reinterpret_cast<uintptr_t>(X) & 15) == 0) {
       const int out_mode = mode == GEMM_ANY_SWIGLU && y_dt == DT_BF16 ? 2 : mode == GEMM_ANY_GEGLU && y_dt == DT_BF16 ? 3
+                           : mode == GEMM_ANY_RELU2 && y_dt == DT_BF16 ? 4
                            : mode == GEMM_ANY_PLAIN ? (y_dt == DT_F32 ? 1 : 0) : -1;
       if (out_mode >= 0 && pnx_gemm_tc(X, Wt, Y, ldy, T, N, K, out_mode)) return;
     }

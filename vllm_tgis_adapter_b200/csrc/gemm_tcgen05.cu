@@ -177,6 +177,14 @@ __device__ __forceinline__ __nv_bfloat16 glu_bf16(int out_mode, float gate_acc, 
   return __float2bfloat16_rn(0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * up_acc);
 }
 
+// Out mode 4: squared ReLU of the accumulator (bf16 out), evaluated in fp32 and rounded once
+__device__ __forceinline__ float ep_act(int out_mode, float v) {
+  if (out_mode != 4) return v;
+  const float z = fmaxf(v, 0.f);
+  return z * z;
+}
+__device__ __forceinline__ bool ep_glu(int out_mode) { return out_mode == 2 || out_mode == 3; }
+
 // Fused RoPE + KV-cache scatter of the qkv projection's final epilogue (tile = one 128-dim head; arithmetic and rounding
 // points of rope_kvwrite_kernel).  Called by a full warp with a warp-uniform (head, t): this thread holds the fp32 sums of
 // dims r4..r4+3 of token t; the rotary partner dims (+-64) live in lane ^ 16.
@@ -566,7 +574,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
           tmem_ld_32x32b_x16(taddr + c0, r);
           tmem_ld_wait();
           if (!partial) {
-            if (out_f32 >= 2) {
+            if (ep_glu(out_f32)) {
               // fused SwiGLU / GeGLU: weight rows are interleaved (2j = gate_j, 2j+1 = up_j) so the pair sits in adjacent
               // lanes; even lanes produce act[t, n/2]
 #pragma unroll
@@ -580,8 +588,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
               for (int j = 0; j < 16; ++j)
                 if (c0 + j < t_valid) {
                   const size_t o = (size_t)(t_base + c0 + j) * ldy + n;
-                  if (out_f32) Yf[o] = __uint_as_float(r[j]);
-                  else Y[o] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                  if (out_f32 == 1) Yf[o] = __uint_as_float(r[j]);
+                  else Y[o] = __float2bfloat16_rn(ep_act(out_f32, __uint_as_float(r[j])));
                 }
             }
           } else {
@@ -687,7 +695,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
                 const float av[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
                 if (rope.positions != nullptr) {  // qkv projection: RoPE + KV scatter (warp-uniform t and tile)
                   qkv_rope_store(rope, nt, t_base + t, r4, av, Y + o);
-                } else if (out_f32 >= 2) {  // fused SwiGLU / GeGLU: rows (n4, n4+1) and (n4+2, n4+3) are (gate, up) pairs
+                } else if (ep_glu(out_f32)) {  // fused SwiGLU / GeGLU: rows (n4, n4+1) and (n4+2, n4+3) are (gate, up) pairs
                   __nv_bfloat16* yo = Y + (size_t)(t_base + t) * ldy + (n4 >> 1);
                   if (n4 + 1 < N) yo[0] = glu_bf16(out_f32, av[0], av[1]);
                   if (n4 + 3 < N) yo[1] = glu_bf16(out_f32, av[2], av[3]);
@@ -695,7 +703,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
                   if (out_f32 == 1) {
                     *reinterpret_cast<float4*>(Yf + o) = acc[j];
                   } else {
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(av[0], av[1]), hi = __floats2bfloat162_rn(av[2], av[3]);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(ep_act(out_f32, av[0]), ep_act(out_f32, av[1])), hi = __floats2bfloat162_rn(ep_act(out_f32, av[2]), ep_act(out_f32, av[3]));
                     uint2 pk;
                     pk.x = *reinterpret_cast<uint32_t*>(&lo);
                     pk.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -704,8 +712,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
                 } else {
                   for (int e = 0; e < 4; ++e)
                     if (n4 + e < N) {
-                      if (out_f32) Yf[o + e] = av[e];
-                      else Y[o + e] = __float2bfloat16_rn(av[e]);
+                      if (out_f32 == 1) Yf[o + e] = av[e];
+                      else Y[o + e] = __float2bfloat16_rn(ep_act(out_f32, av[e]));
                     }
                 }
               }
@@ -842,7 +850,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
               if (lane_id() == 0) norm.sumsq_out[(size_t)t * (N / GEMM_BN) + nt] = ssq;
             } else if (rope.positions != nullptr) {
               qkv_rope_store(rope, nt, t, r4, av, Y + o);
-            } else if (out_f32 >= 2) {
+            } else if (ep_glu(out_f32)) {
               __nv_bfloat16* yo = Y + (size_t)t * ldy + (n4 >> 1);
               if (n4 + 1 < N) yo[0] = glu_bf16(out_f32, av[0], av[1]);
               if (n4 + 3 < N) yo[1] = glu_bf16(out_f32, av[2], av[3]);
@@ -850,7 +858,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
               if (out_f32 == 1) {
                 *reinterpret_cast<float4*>(Yf + o) = acc[j];
               } else {
-                __nv_bfloat162 lo = __floats2bfloat162_rn(av[0], av[1]), hi = __floats2bfloat162_rn(av[2], av[3]);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(ep_act(out_f32, av[0]), ep_act(out_f32, av[1])), hi = __floats2bfloat162_rn(ep_act(out_f32, av[2]), ep_act(out_f32, av[3]));
                 uint2 pk;
                 pk.x = *reinterpret_cast<uint32_t*>(&lo);
                 pk.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -859,8 +867,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_
             } else {
               for (int e = 0; e < 4; ++e)
                 if (n4 + e < N) {
-                  if (out_f32) Yf[o + e] = av[e];
-                  else Y[o + e] = __float2bfloat16_rn(av[e]);
+                  if (out_f32 == 1) Yf[o + e] = av[e];
+                  else Y[o + e] = __float2bfloat16_rn(ep_act(out_f32, av[e]));
                 }
             }
           }

@@ -381,18 +381,20 @@ conv_state_save_kernel(const float* __restrict__ x, int ld, int n, int taps, con
 // ------------------------------------------------------------------------------------------------ gated delta rule
 // grid (sequences, heads, ceil(vdim / 32)); 256 threads = 32 value columns x DS_LPC lanes.  A column of S is independent of
 // the others (its write u_c needs only its own S[:, c] . k), so DS_LPC neighbouring lanes share one column, lane `sub` keeping
-// rows sub, sub + DS_LPC, ... in registers; the two sums over the rows that a token needs -- (g S)[:, c] . k for the write and
+// rows 32 jj + 4 sub + (0..3) in registers; the two sums over the rows that a token needs -- (g S)[:, c] . k for the write and
 // (g S)[:, c] . q for the read-out, which with the write becomes o_c = (g S)[:, c] . q + u_c (k . q) -- meet through one round of
-// shuffles.  Normalised q / k, the decays and the per-token scalars are staged in shared memory DS_CHUNK tokens at a time; the
-// token loop itself runs without a barrier.
+// shuffles.  Normalised q / k, the decays and the per-token scalars are staged in shared memory DS_CHUNK tokens at a time (rows
+// padded to a multiple of four with zeros, so a lane fetches its four rows of each vector with one 16-byte load); the token
+// loop itself runs without a barrier.
 constexpr int DS_LPC = 8, DS_COLS = 32, DS_THREADS = DS_LPC * DS_COLS, DS_CHUNK = 16;
 template <int RPT>
 __global__ void __launch_bounds__(DS_THREADS)
 delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ tok_slot) {
-  extern __shared__ float ds_smem[];
-  const int D = a.dim;
-  float* vec = ds_smem;                                  // [DS_CHUNK][3][D]: q | k | decay
-  float* vcol = vec + (size_t)DS_CHUNK * 3 * D;          // [DS_CHUNK][DS_COLS]
+  extern __shared__ __align__(16) float ds_smem[];
+  static_assert(RPT % 4 == 0, "a lane owns whole groups of four rows");
+  const int D = a.dim, Dp = (D + 3) & ~3;
+  float* vec = ds_smem;                                  // [DS_CHUNK][3][Dp]: q | k | decay
+  float* vcol = vec + (size_t)DS_CHUNK * 3 * Dp;         // [DS_CHUNK][DS_COLS]
   __shared__ float beta_s[DS_CHUNK], kq_s[DS_CHUNK];
   griddep_launch();
   griddep_wait();
@@ -408,20 +410,21 @@ delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   float* Sg = a.S + (((size_t)slot * a.heads + h) * D) * a.vdim + (col_ok ? c : 0);
 #pragma unroll
   for (int j = 0; j < RPT; ++j) {
-    const int i = sub + j * DS_LPC;
+    const int i = (j >> 2) * 32 + sub * 4 + (j & 3);
     S[j] = (!fresh && col_ok && i < D) ? Sg[(size_t)i * a.vdim] : 0.f;
   }
   const float rate = -expf(a.A_log[h]), q_mult = 1.f / sqrtf((float)D);
   for (int t0 = 0; t0 < sq.q_len; t0 += DS_CHUNK) {
     const int nt = min(DS_CHUNK, sq.q_len - t0);
     __syncthreads();   // the previous chunk's vectors are consumed
-    for (int idx = tid; idx < nt * D; idx += DS_THREADS) {
-      const int tt = idx / D, i = idx % D;
+    for (int idx = tid; idx < nt * Dp; idx += DS_THREADS) {
+      const int tt = idx / Dp, i = idx % Dp;
       const size_t row = (size_t)(sq.q_start + t0 + tt);
-      float* v3 = vec + (size_t)tt * 3 * D;
-      v3[i] = a.q[row * a.ldq + (size_t)hq * D + i];
-      v3[D + i] = a.k[row * a.ldk + (size_t)hq * D + i];
-      v3[2 * D + i] = expf(rate * softplus_f(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.decay_b[(size_t)h * D + i]));
+      float* v3 = vec + (size_t)tt * 3 * Dp;
+      const bool in = i < D;
+      v3[i] = in ? a.q[row * a.ldq + (size_t)hq * D + i] : 0.f;
+      v3[Dp + i] = in ? a.k[row * a.ldk + (size_t)hq * D + i] : 0.f;
+      v3[2 * Dp + i] = in ? expf(rate * softplus_f(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.decay_b[(size_t)h * D + i])) : 0.f;
     }
     for (int idx = tid; idx < nt * DS_COLS; idx += DS_THREADS) {
       const int tt = idx / DS_COLS, cc = idx % DS_COLS, col = blockIdx.z * DS_COLS + cc;
@@ -430,28 +433,41 @@ delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     if (tid < nt) beta_s[tid] = sigmoid_f(a.beta_raw[(size_t)(sq.q_start + t0 + tid) * a.ldb + h]);
     __syncthreads();
     for (int tt = warp; tt < nt; tt += DS_THREADS / 32) {   // unit vectors, and k . q of the unit vectors
-      float* v3 = vec + (size_t)tt * 3 * D;
+      float* v3 = vec + (size_t)tt * 3 * Dp;
       float sq2 = 0.f, sk2 = 0.f, skq = 0.f;
       for (int i = lane; i < D; i += 32) {
-        const float qv = v3[i], kv = v3[D + i];
+        const float qv = v3[i], kv = v3[Dp + i];
         sq2 = fmaf(qv, qv, sq2); sk2 = fmaf(kv, kv, sk2); skq = fmaf(qv, kv, skq);
       }
       sq2 = warp_sum_f(sq2); sk2 = warp_sum_f(sk2); skq = warp_sum_f(skq);
       const float rq = q_mult / sqrtf(sq2 + 1e-6f), rk = 1.f / sqrtf(sk2 + 1e-6f);
-      for (int i = lane; i < D; i += 32) { v3[i] *= rq; v3[D + i] *= rk; }
+      for (int i = lane; i < D; i += 32) { v3[i] *= rq; v3[Dp + i] *= rk; }
       if (lane == 0) kq_s[tt] = skq * rq * rk;
     }
     __syncthreads();
     for (int tt = 0; tt < nt; ++tt) {
-      const float* v3 = vec + (size_t)tt * 3 * D;
+      const float* v3 = vec + (size_t)tt * 3 * Dp;
+      float kr[RPT];
       float sk = 0.f, sqv = 0.f;
 #pragma unroll
-      for (int j = 0; j < RPT; ++j) {
-        const int i = sub + j * DS_LPC;
-        if (i < D) {
-          S[j] *= v3[2 * D + i];
-          sk = fmaf(S[j], v3[D + i], sk);
-          sqv = fmaf(S[j], v3[i], sqv);
+      for (int jj = 0; jj < RPT / 4; ++jj) {
+        const int i0 = jj * 32 + sub * 4;
+        if (i0 < Dp) {
+          const float4 q4 = *reinterpret_cast<const float4*>(v3 + i0);
+          const float4 k4 = *reinterpret_cast<const float4*>(v3 + Dp + i0);
+          const float4 g4 = *reinterpret_cast<const float4*>(v3 + 2 * Dp + i0);
+          const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w}, ga[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = jj * 4 + e;
+            S[j] *= ga[e];
+            sk = fmaf(S[j], ka[e], sk);
+            sqv = fmaf(S[j], qa[e], sqv);
+            kr[j] = ka[e];
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) kr[jj * 4 + e] = 0.f;
         }
       }
 #pragma unroll
@@ -461,17 +477,14 @@ delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       }
       const float u = beta_s[tt] * (vcol[tt * DS_COLS + cl] - sk);
 #pragma unroll
-      for (int j = 0; j < RPT; ++j) {
-        const int i = sub + j * DS_LPC;
-        if (i < D) S[j] = fmaf(v3[D + i], u, S[j]);
-      }
+      for (int j = 0; j < RPT; ++j) S[j] = fmaf(kr[j], u, S[j]);
       if (sub == 0 && col_ok) a.out[(size_t)(sq.q_start + t0 + tt) * a.ldo + (size_t)h * a.vdim + c] = fmaf(u, kq_s[tt], sqv);
     }
   }
   if (col_ok) {
 #pragma unroll
     for (int j = 0; j < RPT; ++j) {
-      const int i = sub + j * DS_LPC;
+      const int i = (j >> 2) * 32 + sub * 4 + (j & 3);
       if (i < D) Sg[(size_t)i * a.vdim] = S[j];
     }
   }
@@ -508,6 +521,36 @@ head_norm_gate_kernel(const float* __restrict__ o, int ldo, int heads, int vdim,
     const float gl = gate[(size_t)t * ldg + (size_t)h * vdim + i];
     const float gv = act == 1 ? silu_f(gl) : sigmoid_f(gl);
     st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * rs * w[(size_t)h * vdim + i] * gv);
+  }
+}
+
+// wide groups (a whole row normed as one or a few groups): grid (T, heads), 256 threads, one CTA per (token, group)
+__global__ void __launch_bounds__(256)
+head_norm_gate_wide_kernel(const float* __restrict__ o, int ldo, int heads, int vdim, const float* __restrict__ w,
+                           const float* __restrict__ gate, int ldg, int act, float eps, void* __restrict__ out, int out_dtype,
+                           int out_ld, int gate_first) {
+  __shared__ float red[8];
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const float* orow = o + (size_t)t * ldo + (size_t)h * vdim;
+  const float* grow = gate + (size_t)t * ldg + (size_t)h * vdim;
+  float ss = 0.f;
+  for (int i = tid; i < vdim; i += 256) {
+    float v = orow[i];
+    if (gate_first) v *= act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum_f(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) tot += red[r];   // the same order in every thread
+  const float rs = 1.f / sqrtf(tot / (float)vdim + eps);
+  for (int i = tid; i < vdim; i += 256) {
+    const float gv = act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
+    st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * gv * rs * w[(size_t)h * vdim + i]);
   }
 }
 
@@ -590,6 +633,9 @@ cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, 
                                   int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream,
                                   int gate_first) {
   if (T <= 0) return cudaSuccess;
+  if (vdim >= 1024 && heads <= 65535)
+    return launch_k(head_norm_gate_wide_kernel, dim3(T, heads), dim3(256), 0, stream, o, ldo, heads, vdim, w, gate, ldg, act, eps, out,
+                    out_dtype, heads * vdim, gate_first);
   return launch_k(head_norm_gate_kernel, dim3(T, (heads + 3) / 4), dim3(128), 0, stream, o, ldo, heads, vdim, w, gate, ldg, act,
                   eps, out, out_dtype, heads * vdim, gate_first);
 }
@@ -604,7 +650,7 @@ cudaError_t conv_state_save_launch(const float* x, int ld, int n, int taps, cons
 template <int RPT>
 static cudaError_t delta_scan_rpt(const DeltaScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot, cudaStream_t stream) {
   const dim3 grid(n_seqs, a.heads, (a.vdim + DS_COLS - 1) / DS_COLS);
-  const size_t smem = ((size_t)DS_CHUNK * 3 * a.dim + DS_CHUNK * DS_COLS) * sizeof(float);
+  const size_t smem = ((size_t)DS_CHUNK * 3 * ((a.dim + 3) & ~3) + DS_CHUNK * DS_COLS) * sizeof(float);
   if (smem > 48 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
@@ -621,6 +667,7 @@ cudaError_t delta_scan_launch(const DeltaScan& a, const AttnSeq* seqs, int n_seq
   if (a.dim < 1 || a.dim > DELTA_SCAN_MAX_DIM || a.heads < 1 || a.heads > 65535 || a.vdim < 1 || a.qk_heads < 1 ||
       a.heads % a.qk_heads != 0)
     return cudaErrorInvalidValue;
+  if (a.dim <= 32) return delta_scan_rpt<4>(a, seqs, n_seqs, tok_slot, stream);
   if (a.dim <= 8 * DS_LPC) return delta_scan_rpt<8>(a, seqs, n_seqs, tok_slot, stream);
   if (a.dim <= 16 * DS_LPC) return delta_scan_rpt<16>(a, seqs, n_seqs, tok_slot, stream);
   return delta_scan_rpt<32>(a, seqs, n_seqs, tok_slot, stream);
