@@ -169,6 +169,12 @@ int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ld
                       int32_t ldd, const float* decay_b, const float* A_log, const float* beta_raw, int32_t ldb, float* S,
                       float* out, int32_t ldo, int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim,
                       const int32_t* seqs_host, int32_t n_seqs, const int32_t* tok_slot);
+/* csrc/recurrent.cu outer_scan_kernel in OUTER_SCAN_SSD mode: q = C, k = B [T, qk_heads * dim], v = x [T, heads * vdim], one step
+ * size per head and token (step_raw [T, heads] + step_b), S [slots][heads][dim][vdim] */
+int tgis_k_ssd_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* step_raw,
+                    int32_t lds, const float* step_b, const float* A_log, const float* D, float* S, float* out, int32_t ldo,
+                    int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim, const int32_t* seqs_host, int32_t n_seqs,
+                    const int32_t* tok_slot);
 int tgis_k_capattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const tgis_k_capattn_geom* g,
                         const float* w_q, const float* w_k, float eps, const int32_t* positions, const int32_t* slots,
                         void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T);

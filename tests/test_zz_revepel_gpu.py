@@ -234,6 +234,38 @@ def test_delta_rule_scan_in_portions_and_two_slots_matches_oracle():
             assert err < 5e-5, (H, G, d, dv, r, err)
 
 
+def test_state_space_scan_in_portions_and_two_slots_matches_oracle():
+    """outer_scan_kernel's state-space mode against the oracle's mamba2 with selector projections, a one-tap convolution of
+    weight one and unit norm weight: what is compared is the gated, RMS-normed read-out."""
+    from oracle import revepel_oracle as O
+
+    for (H, G, N, P, T) in ((6, 3, 5, 4, 70), (4, 1, 64, 40, 50), (2, 2, 200, 33, 40), (1, 1, 1, 1, 20)):
+        eps, inner, gn = 1e-5, H * P, G * N
+        gen = torch.Generator().manual_seed(H * 100 + N)
+        width = 2 * inner + 2 * gn + H
+        m = dict(heads=H, vdim=P, state=N, groups=G, norm_groups=1, conv=1)
+        w = {"in": torch.eye(width, dtype=F64), "conv": torch.ones(inner + 2 * gn, 1, dtype=F64), "conv.b": torch.zeros(inner + 2 * gn, dtype=F64),
+             "dt_bias": torch.randn(H, generator=gen, dtype=F64) - 1.0, "A_log": torch.randn(H, generator=gen, dtype=F64) * 0.3,
+             "D": torch.randn(H, generator=gen, dtype=F64), "norm": torch.ones(inner, dtype=F64), "o": torch.eye(inner, dtype=F64)}
+        hs = [torch.randn(T, width, generator=gen, dtype=F64).float().double() for _ in range(2)]
+        refs = [O.mamba2(h, w, m, eps) for h in hs]
+        S = torch.full((3, H, N, P), float("nan"), device="cuda")
+        outs = [torch.zeros(T, inner, device="cuda") for _ in range(2)]
+        for at, n in _portions(T, [5, 1, 2, 17, 1]):
+            for r, slot in ((0, 1), (1, 2)):
+                h = hs[r][at:at + n]
+                act = O.silu(h[:, inner:2 * inner + 2 * gn])      # x | B | C after the one-tap convolution
+                o = torch.zeros(n, inner, device="cuda")
+                _ok(_lib().tgis_k_ssd_scan(_p(_dev(act[:, inner + gn:])), _p(_dev(act[:, inner:inner + gn])), _p(_dev(act[:, :inner])), gn, gn,
+                                           inner, _p(_dev(h[:, 2 * inner + 2 * gn:])), H, _p(_dev(w["dt_bias"])), _p(_dev(w["A_log"])),
+                                           _p(_dev(w["D"])), _p(S), _p(o), inner, H, G, N, P, _ints([0, n, at + n, 0]), 1, _p(_i32([slot] * n))))
+                outs[r][at:at + n] = o
+        for r in range(2):
+            got = O.rms(outs[r].double().cpu() * O.silu(hs[r][:, :inner]), eps)
+            err = float((got - refs[r]).abs().max() / refs[r].abs().max())
+            assert err < 5e-5, (H, G, N, P, r, err)
+
+
 # ====================================================================================================== engine
 def _moe(experts, top, ff, shared=0):
     m = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}}

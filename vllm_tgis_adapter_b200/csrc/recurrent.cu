@@ -414,24 +414,58 @@ delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     S[j] = (!fresh && col_ok && i < D) ? Sg[(size_t)i * a.vdim] : 0.f;
   }
   const float rate = -expf(a.A_log[h]), q_mult = 1.f / sqrtf((float)D);
+  // A chunk's raw values travel global memory -> registers -> shared memory: all loads of a chunk are issued back to back
+  // (one round trip to memory, not one per element), and the loads of chunk n + 1 are issued before the token loop of chunk n.
+  // thread (tt = tid / 16, l = tid % 16) stages entries l, l + 16, ... of token tt's vectors, and two of the chunk's values
+  constexpr int EPT = RPT / 2;   // 8 RPT rows at most, 16 threads per token
+  constexpr int TPT = DS_THREADS / DS_CHUNK;
+  static_assert(TPT == 16 && DS_CHUNK * DS_COLS == 2 * DS_THREADS, "staging map");
+  const int st_tt = tid / TPT, st_l = tid % TPT;
+  float pq[EPT], pk[EPT], pd[EPT], pv[2], pb = 0.f;
+  auto fetch = [&](int t0) {
+    const int nt = min(DS_CHUNK, sq.q_len - t0);
+    const bool tok = st_tt < nt;
+    const size_t row = (size_t)(sq.q_start + t0 + (tok ? st_tt : 0));
+    const float* qr = a.q + row * a.ldq + (size_t)hq * D;
+    const float* kr_ = a.k + row * a.ldk + (size_t)hq * D;
+    const float* dr = a.decay_raw + row * a.ldd + (size_t)h * D;
+    const float* db = a.decay_b + (size_t)h * D;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const int i = st_l + e * TPT;
+      const bool in = tok && i < D;
+      pq[e] = in ? qr[i] : 0.f;
+      pk[e] = in ? kr_[i] : 0.f;
+      pd[e] = in ? dr[i] + db[i] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {   // value columns: token tt, columns 2 l + e
+      const int col = blockIdx.z * DS_COLS + 2 * st_l + e;
+      pv[e] = (tok && col < a.vdim) ? a.v[row * a.ldv + (size_t)h * a.vdim + col] : 0.f;
+    }
+    pb = tid < nt ? a.beta_raw[(size_t)(sq.q_start + t0 + tid) * a.ldb + h] : 0.f;
+  };
+  fetch(0);
   for (int t0 = 0; t0 < sq.q_len; t0 += DS_CHUNK) {
     const int nt = min(DS_CHUNK, sq.q_len - t0);
     __syncthreads();   // the previous chunk's vectors are consumed
-    for (int idx = tid; idx < nt * Dp; idx += DS_THREADS) {
-      const int tt = idx / Dp, i = idx % Dp;
-      const size_t row = (size_t)(sq.q_start + t0 + tt);
-      float* v3 = vec + (size_t)tt * 3 * Dp;
-      const bool in = i < D;
-      v3[i] = in ? a.q[row * a.ldq + (size_t)hq * D + i] : 0.f;
-      v3[Dp + i] = in ? a.k[row * a.ldk + (size_t)hq * D + i] : 0.f;
-      v3[2 * Dp + i] = in ? expf(rate * softplus_f(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.decay_b[(size_t)h * D + i])) : 0.f;
+    if (st_tt < nt) {
+      float* v3 = vec + (size_t)st_tt * 3 * Dp;
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const int i = st_l + e * TPT;
+        if (i < Dp) {
+          v3[i] = pq[e];
+          v3[Dp + i] = pk[e];
+          v3[2 * Dp + i] = i < D ? expf(rate * softplus_f(pd[e])) : 0.f;
+        }
+      }
     }
-    for (int idx = tid; idx < nt * DS_COLS; idx += DS_THREADS) {
-      const int tt = idx / DS_COLS, cc = idx % DS_COLS, col = blockIdx.z * DS_COLS + cc;
-      vcol[idx] = col < a.vdim ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + col] : 0.f;
-    }
-    if (tid < nt) beta_s[tid] = sigmoid_f(a.beta_raw[(size_t)(sq.q_start + t0 + tid) * a.ldb + h]);
+    vcol[st_tt * DS_COLS + 2 * st_l] = pv[0];
+    vcol[st_tt * DS_COLS + 2 * st_l + 1] = pv[1];
+    if (tid < nt) beta_s[tid] = sigmoid_f(pb);
     __syncthreads();
+    if (t0 + DS_CHUNK < sq.q_len) fetch(t0 + DS_CHUNK);   // lands while this chunk's tokens are worked through
     for (int tt = warp; tt < nt; tt += DS_THREADS / 32) {   // unit vectors, and k . q of the unit vectors
       float* v3 = vec + (size_t)tt * 3 * Dp;
       float sq2 = 0.f, sk2 = 0.f, skq = 0.f;
@@ -445,8 +479,8 @@ delta_scan_kernel(DeltaScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       if (lane == 0) kq_s[tt] = skq * rq * rk;
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* v3 = vec + (size_t)tt * 3 * Dp;
+    const float* v3 = vec;
+    for (int tt = 0; tt < nt; ++tt, v3 += 3 * Dp) {
       float kr[RPT];
       float sk = 0.f, sqv = 0.f;
 #pragma unroll

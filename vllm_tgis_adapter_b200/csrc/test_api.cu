@@ -692,6 +692,23 @@ int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ld
   return 0;
 }
 
+int tgis_k_ssd_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* step_raw,
+                    int32_t lds, const float* step_b, const float* A_log, const float* D, float* S, float* out, int32_t ldo,
+                    int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim, const int32_t* seqs_host, int32_t n_seqs,
+                    const int32_t* tok_slot) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  Tmp<AttnSeq> d_seqs;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  OuterScan a{};
+  a.mode = OUTER_SCAN_SSD; a.q = q; a.k = k; a.v = v; a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.q_scale = 1.f;
+  a.step_raw = step_raw; a.lds = lds; a.step_b = step_b; a.A_log = A_log; a.D = D;
+  a.S = S; a.out = out; a.ldo = ldo; a.heads = heads; a.qk_heads = qk_heads; a.dim = dim; a.vdim = vdim;
+  KCK(outer_scan_launch(a, d_seqs.p, n_seqs, tok_slot, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
 int tgis_k_token_shift(const float* x, int32_t width, const float* mu, int32_t n_mix, const int32_t* positions,
                        const int32_t* tok_slot, const float* prev_state, void* out, int32_t out_dt, int64_t out_bs, int32_t T) {
   KCK(token_shift_mix_launch(x, width, mu, n_mix, positions, tok_slot, prev_state, out, out_dt, out_bs, T, 0));

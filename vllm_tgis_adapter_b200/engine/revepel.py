@@ -260,7 +260,7 @@ def synthetic_weights(mc: ModelConfig, seed: int, device: str = "cpu") -> dict:
     return dict(iter_synthetic_weights(mc, seed, device))
 
 
-def _moe(width: int, experts: int, top: int, ff: int, shared: int) -> dict:
+def _moe(experts: int, top: int, ff: int, shared: int) -> dict:
     return dict(experts=experts, top=top, expert_ff=ff, shared_ff=shared)
 
 
@@ -279,20 +279,20 @@ def _attn(heads: int, kv_heads: int, dim: int, window: int, kv_from: int | None 
 # reads the first one's keys and values; every layer with experts whose ACTIVE width per token equals the Llama twin's
 PRESETS: dict[str, ModelConfig] = {
     "revepel-tiny": _stack(128, 512, [
-        LayerSpec("channel_delta", heads=4, kv_heads=2, dim=16, vdim=24, conv=4, decay_rank=8, gate_rank=12, **_moe(128, 6, 2, 48, 80)),
+        LayerSpec("channel_delta", heads=4, kv_heads=2, dim=16, vdim=24, conv=4, decay_rank=8, gate_rank=12, **_moe(6, 2, 48, 80)),
         LayerSpec("attention", heads=4, kv_heads=2, dim=32, vdim=48, window=24, scale=0.2, rot_dims=16, rot_base=1000.0,
-                  yarn=(4.0, 64.0, 8.0, 1.0), **_moe(128, 6, 2, 48, 0)),
+                  yarn=(4.0, 64.0, 8.0, 1.0), **_moe(6, 2, 48, 0)),
         LayerSpec("mamba2", heads=4, vdim=40, state=24, groups=2, norm_groups=2, conv=3),
         LayerSpec("attention", heads=4, kv_heads=2, dim=32, vdim=48, window=7, scale=0.2, rot_dims=16, rot_base=1000.0,
-                  yarn=(4.0, 64.0, 8.0, 1.0), kv_from=1, **_moe(128, 5, 1, 64, 32))]),
+                  yarn=(4.0, 64.0, 8.0, 1.0), kv_from=1, **_moe(5, 1, 64, 32))]),
     "revepel-1k": _stack(1024, 32768, [
-        LayerSpec("channel_delta", heads=8, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64, **_moe(1024, 16, 2, 1024, 1024)),
-        _attn(8, 2, 128, 2048, **_moe(1024, 16, 2, 1024, 1024)),
-        LayerSpec("mamba2", heads=32, vdim=64, state=128, groups=1, norm_groups=1, conv=4, **_moe(1024, 16, 2, 1024, 1024)),
-        _attn(8, 2, 128, 2048, kv_from=1, **_moe(1024, 16, 2, 1024, 1024))]),
+        LayerSpec("channel_delta", heads=8, kv_heads=8, dim=128, vdim=128, conv=4, decay_rank=64, gate_rank=64, **_moe(16, 2, 1024, 1024)),
+        _attn(8, 2, 128, 2048, **_moe(16, 2, 1024, 1024)),
+        LayerSpec("mamba2", heads=32, vdim=64, state=128, groups=1, norm_groups=1, conv=4, **_moe(16, 2, 1024, 1024)),
+        _attn(8, 2, 128, 2048, kv_from=1, **_moe(16, 2, 1024, 1024))]),
     "revepel-2k": _stack(2048, 32768, [
-        LayerSpec("channel_delta", heads=16, kv_heads=16, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128, **_moe(2048, 64, 6, 1408, 2816)),
-        _attn(16, 4, 128, 4096, **_moe(2048, 64, 6, 1408, 2816)),
-        LayerSpec("mamba2", heads=64, vdim=64, state=128, groups=1, norm_groups=1, conv=4, **_moe(2048, 64, 6, 1408, 2816)),
-        _attn(16, 4, 128, 4096, kv_from=1, **_moe(2048, 64, 6, 1408, 2816))]),
+        LayerSpec("channel_delta", heads=16, kv_heads=16, dim=128, vdim=128, conv=4, decay_rank=128, gate_rank=128, **_moe(64, 6, 1408, 2816)),
+        _attn(16, 4, 128, 4096, **_moe(64, 6, 1408, 2816)),
+        LayerSpec("mamba2", heads=64, vdim=64, state=128, groups=1, norm_groups=1, conv=4, **_moe(64, 6, 1408, 2816)),
+        _attn(16, 4, 128, 4096, kv_from=1, **_moe(64, 6, 1408, 2816))]),
 }
