@@ -54,6 +54,8 @@ token_shift_mix_kernel(const float* __restrict__ x, int width, const float* __re
 }
 
 // ------------------------------------------------------------------------------------------------ short convolution
+// VEC channels per thread (VEC = 4: 16-byte loads and stores; needs ld, inner and every base pointer aligned to four floats)
+template <int VEC>
 __global__ void __launch_bounds__(128)
 short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const float* __restrict__ w,
                        const float* __restrict__ b, int taps, const int32_t* __restrict__ positions,
@@ -61,21 +63,38 @@ short_conv_silu_kernel(const float* __restrict__ xz, int ld, int inner, const fl
                        float* __restrict__ out_f32, void* __restrict__ out_op, int out_dtype) {
   griddep_launch();
   griddep_wait();
-  const int t = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+  const int t = blockIdx.x, c = (blockIdx.y * 128 + threadIdx.x) * VEC;
   if (c >= inner) return;
   const int slot = tok_slot[t], p = positions[t];
   int nb = 0;  // predecessors of this token inside the batch (as far as the taps reach)
   while (nb < taps - 1 && t - nb - 1 >= 0 && tok_slot[t - nb - 1] == slot) ++nb;
-  float acc = b != nullptr ? b[c] : 0.f;
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = b != nullptr ? b[c + e] : 0.f;
   for (int j = taps - 1; j >= 0; --j) {   // oldest input first
     if (p - j < 0) continue;
-    const float v = j <= nb ? xz[(size_t)(t - j) * ld + c]
-                            : conv_state[((size_t)slot * (taps - 1) + (taps - 1 - j + nb)) * inner + c];
-    acc = fmaf(w[(size_t)c * taps + (taps - 1 - j)], v, acc);
+    const float* src = j <= nb ? xz + (size_t)(t - j) * ld + c
+                               : conv_state + ((size_t)slot * (taps - 1) + (taps - 1 - j + nb)) * inner + c;
+    float v[VEC];
+    if (VEC == 4) {
+      const float4 q = *reinterpret_cast<const float4*>(src);
+      v[0] = q.x; v[1 % VEC] = q.y; v[2 % VEC] = q.z; v[3 % VEC] = q.w;
+    } else {
+      v[0] = *src;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = fmaf(w[(size_t)(c + e) * taps + (taps - 1 - j)], v[e], acc[e]);
   }
-  const float y = silu_f(acc);
-  if (out_f32) out_f32[(size_t)t * inner + c] = y;
-  if (out_op) st_op(out_op, out_dtype, (size_t)t * inner + c, y);
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+  if (out_f32) {
+    if (VEC == 4) *reinterpret_cast<float4*>(out_f32 + (size_t)t * inner + c) = make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
+    else out_f32[(size_t)t * inner + c] = acc[0];
+  }
+  if (out_op) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) st_op(out_op, out_dtype, (size_t)t * inner + c + e, acc[e]);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ selective scan
@@ -245,31 +264,67 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     }
     m_run = fresh ? 0.f : a.m[(size_t)slot * a.heads + h];
   }
+  // A chunk's raw values travel global memory -> registers -> shared memory: thread (tt = tid / 16, l = tid % 16) stages entries
+  // l, l + 16, ... of token tt's vectors and two of its value columns, all loads of a chunk are issued back to back, and the
+  // loads of chunk n + 1 are issued before the token loop of chunk n.
+  constexpr int EPT = RPT / 2, TPT = OS_THREADS / OS_CHUNK;
+  static_assert(TPT == 16 && OS_CHUNK * OS_COLS == 2 * OS_THREADS, "staging map");
+  const int st_tt = tid / TPT, st_l = tid % TPT;
+  float pq[EPT], pk[EPT], pd[EPT], pv[2], pg0 = 0.f, pg1 = 0.f;
+  auto fetch = [&](int t0) {
+    const int nt = min(OS_CHUNK, sq.q_len - t0);
+    const bool tok = st_tt < nt;
+    const size_t row = (size_t)(sq.q_start + t0 + (tok ? st_tt : 0));
+    const float* qr = a.q + row * a.ldq + (size_t)hq * D;
+    const float* kr = a.k + row * a.ldk + (size_t)hq * D;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+      const int i = st_l + e * TPT;
+      const bool in = tok && i < D;
+      pq[e] = in ? qr[i] : 0.f;
+      pk[e] = in ? kr[i] : 0.f;
+      if (MODE == OUTER_SCAN_DECAY) pd[e] = in ? a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int col = c0 + 2 * st_l + e;
+      pv[e] = (tok && col < a.vdim) ? a.v[row * a.ldv + (size_t)h * a.vdim + col] : 0.f;
+    }
+    if (tid < nt) {
+      const size_t grow = (size_t)(sq.q_start + t0 + tid);
+      if (MODE == OUTER_SCAN_GATED) { pg0 = a.ig[grow * a.ldg + h]; pg1 = a.fg[grow * a.ldg + h]; }
+      if (MODE == OUTER_SCAN_SSD) pg0 = a.step_raw[grow * a.lds + h];
+    }
+  };
+  fetch(0);
   for (int t0 = 0; t0 < sq.q_len; t0 += OS_CHUNK) {
     const int nt = min(OS_CHUNK, sq.q_len - t0);
     __syncthreads();   // the previous chunk's vectors and partial sums are consumed
-    for (int idx = tid; idx < nt * D; idx += OS_THREADS) {
-      const int tt = idx / D, i = idx % D;
-      const size_t row = (size_t)(sq.q_start + t0 + tt);
-      float* v3 = vec + (size_t)tt * 3 * D;
-      v3[i] = a.q[row * a.ldq + (size_t)hq * D + i] * a.q_scale;
-      v3[D + i] = a.k[row * a.ldk + (size_t)hq * D + i];
-      if (MODE == OUTER_SCAN_DECAY)
-        v3[2 * D + i] = expf(-expf(a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i]));
+    if (st_tt < nt) {
+      float* v3 = vec + (size_t)st_tt * 3 * D;
+#pragma unroll
+      for (int e = 0; e < EPT; ++e) {
+        const int i = st_l + e * TPT;
+        if (i < D) {
+          v3[i] = pq[e] * a.q_scale;
+          v3[D + i] = pk[e];
+          if (MODE == OUTER_SCAN_DECAY) v3[2 * D + i] = expf(-expf(pd[e]));
+        }
+      }
     }
-    for (int tt = g; tt < nt; tt += OS_GROUPS)
-      vcol[tt * OS_COLS + lane] = col_ok ? a.v[(size_t)(sq.q_start + t0 + tt) * a.ldv + (size_t)h * a.vdim + c] : 0.f;
+    vcol[st_tt * OS_COLS + 2 * st_l] = pv[0];
+    vcol[st_tt * OS_COLS + 2 * st_l + 1] = pv[1];
     if (MODE == OUTER_SCAN_GATED && tid < nt) {
-      const size_t row = (size_t)(sq.q_start + t0 + tid);
-      gates[tid][0] = a.gate_cap * tanhf((a.ig[row * a.ldg + h] + a.ig_b[h]) / a.gate_cap);
-      gates[tid][1] = logsigmoid_f(a.gate_cap * tanhf((a.fg[row * a.ldg + h] + a.fg_b[h]) / a.gate_cap));
+      gates[tid][0] = a.gate_cap * tanhf((pg0 + a.ig_b[h]) / a.gate_cap);
+      gates[tid][1] = logsigmoid_f(a.gate_cap * tanhf((pg1 + a.fg_b[h]) / a.gate_cap));
     }
     if (MODE == OUTER_SCAN_SSD && tid < nt) {   // the token's step size and the decay it gives
-      const float dt = softplus_f(a.step_raw[(size_t)(sq.q_start + t0 + tid) * a.lds + h] + a.step_b[h]);
+      const float dt = softplus_f(pg0 + a.step_b[h]);
       gates[tid][0] = expf(ssd_rate * dt);
       gates[tid][1] = dt;
     }
     __syncthreads();
+    if (t0 + OS_CHUNK < sq.q_len) fetch(t0 + OS_CHUNK);   // lands while this chunk's tokens are worked through
     for (int tt = 0; tt < nt; ++tt) {
       const float* v3 = vec + (size_t)tt * 3 * D;
       const float vc = vcol[tt * OS_COLS + lane];
@@ -610,7 +665,11 @@ cudaError_t short_conv_silu_launch(const float* xz, int ld, int inner, const flo
                                    float* out_f32, void* out_op, int out_dtype, int T, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
   if (taps < 1) return cudaErrorInvalidValue;
-  return launch_k(short_conv_silu_kernel, dim3(T, (inner + 127) / 128), dim3(128), 0, stream, xz, ld, inner, w, b, taps,
+  auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (ld % 4 == 0 && inner % 4 == 0 && al16(xz) && al16(conv_state) && al16(out_f32))
+    return launch_k(short_conv_silu_kernel<4>, dim3(T, (inner / 4 + 127) / 128), dim3(128), 0, stream, xz, ld, inner, w, b, taps,
+                    positions, tok_slot, conv_state, out_f32, out_op, out_dtype);
+  return launch_k(short_conv_silu_kernel<1>, dim3(T, (inner + 127) / 128), dim3(128), 0, stream, xz, ld, inner, w, b, taps,
                   positions, tok_slot, conv_state, out_f32, out_op, out_dtype);
 }
 
