@@ -23,7 +23,19 @@ class LiveServer:
         from vllm_tgis_adapter_b200.engine.tokenizer import build_synthetic_tokenizer
         from vllm_tgis_adapter_b200.grpc import grpc_server
 
-        if cfg_name.startswith("opt-"):   # OPT family (tests/test_zz_opt_gpu.py): HF OPT names, no rotary table
+        if cfg_name.startswith("revepel-"):   # layer-list family (tests/test_zz_revepel_gpu.py): preset sizes, seeded CPU weights, fp32
+            import dataclasses
+            import types
+
+            from vllm_tgis_adapter_b200.engine.core import cache_block_bytes
+            from vllm_tgis_adapter_b200.engine.revepel import PRESETS, synthetic_weights as revepel_weights
+
+            mc = dataclasses.replace(PRESETS[cfg_name], max_model_len=256, dtype="float32")
+            self.cfg = c = types.SimpleNamespace(vocab=mc.vocab, model_config=mc)
+            self.weights = revepel_weights(mc, seed)
+            native = NativeEngine(mc, max_num_seqs=8, max_batched_tokens=64, kv_cache_bytes=cache_block_bytes(mc) * 64)
+            native.load_weights(self.weights)
+        elif cfg_name.startswith("opt-"):   # OPT family (tests/test_zz_opt_gpu.py): HF OPT names, no rotary table
             from oracle.opt_oracle import OPT_CONFIGS, synthetic_opt_weights
 
             self.cfg = c = OPT_CONFIGS[cfg_name]

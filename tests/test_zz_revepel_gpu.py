@@ -544,6 +544,43 @@ def test_greedy_generation_through_the_scheduler_matches_oracle():
                 assert abs(r.logprob - float(lp[i, r.new_token])) < 1e-3
 
 
+def test_generate_over_grpc_matches_oracle():
+    """grpc client -> TextGenerationService -> AsyncTGISEngine -> the engine's step loop on a Revepel preset (float32): greedy
+    tokens and their logprobs of a batched Generate call against the oracle."""
+    from test_server_gpu import LiveServer
+
+    from oracle import revepel_oracle as O
+    from vllm_tgis_adapter_b200.engine.revepel import config_json
+    from vllm_tgis_adapter_b200.engine.tokenizer import synthetic_prompt
+    from vllm_tgis_adapter_b200.grpc.pb import generation_pb2 as pb
+
+    srv = LiveServer("revepel-tiny", seed=29)
+    try:
+        cfg = config_json(srv.cfg.model_config)
+        rs = np.random.RandomState(5)
+        prompts = [rs.randint(3, srv.cfg.vocab, size=n).tolist() for n in (12, 70, 7)]     # 70: prefilled in two portions
+        params = pb.Parameters()
+        params.stopping.max_new_tokens = 10
+        params.stopping.min_new_tokens = 10
+        params.response.generated_tokens = True
+        params.response.token_logprobs = True
+        call = srv.channel.unary_unary("/fmaas.GenerationService/Generate",
+                                       request_serializer=pb.BatchedGenerationRequest.SerializeToString,
+                                       response_deserializer=pb.BatchedGenerationResponse.FromString)
+        resp = call(pb.BatchedGenerationRequest(model_id="m", requests=[pb.GenerationRequest(text=synthetic_prompt(p)) for p in prompts],
+                                                params=params), timeout=120)
+    finally:
+        srv.close()
+    assert len(resp.responses) == 3
+    for p, r in zip(prompts, resp.responses):
+        assert r.input_token_count == len(p) and r.generated_token_count == 10
+        got = [int(t.text[1:]) for t in r.tokens]
+        assert got == O.greedy(cfg, srv.weights, p, 10)
+        lp = torch.log_softmax(O.forward(cfg, srv.weights, p + got[:-1])[len(p) - 1:], -1)
+        for i, t in enumerate(r.tokens):
+            assert abs(t.logprob - float(lp[i, got[i]])) < 1e-3
+
+
 def test_trace_runner_command_line_on_a_model_directory(tmp_path):
     """bin/trace_run on a directory with config.json + model.safetensors: the family and the ranks of the low-rank maps come
     from the files, a mixed schedule with a reused slot goes through standard input, the logits land in the output folder."""
