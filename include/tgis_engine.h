@@ -39,7 +39,7 @@
 extern "C" {
 #endif
 
-#define TGIS_ABI_VERSION 10
+#define TGIS_ABI_VERSION 11
 #define TGIS_MAX_REQUEST_ID 96
 #define TGIS_MAX_TOPN 12 /* reference forces max_logprobs >= 11: tgis_utils/args.py:214-216 */
 #define TGIS_MAX_STOP_TOKEN_IDS 8
@@ -81,6 +81,18 @@ typedef struct tgis_engine tgis_engine;
  *          squared-ReLU experts whose INPUT is weighted, and a shared expert (TGIS_MLP_MOE_SIGMOID).  Logits times
  *          logit_scale.  bf16 or fp32 operands.  Single GPU, no LoRA slots. */
 #define TGIS_ARCH_REVEPEL 4
+
+/*   SIKAZEN: a layer list as well (tgis_engine_create_spec), fp32 residual stream.  A layer has two norms that carry ONE number
+ *          each; its mixer and its feed-forward read the same stream and are added together (TGIS_STYLE_PARALLEL_PAIR):
+ *          x += mixer(rms(x) g1) + ff(rms(x) g2); then a per-layer token input is added: x += rms(P (gelu(G x) * e)) * w with e
+ *          the layer's slice of the token's row of a side table.  A span of layers may run several passes in a row on the same
+ *          weights (loop_start / loop_stop / loop_times), every pass with cache rows and state of its own; the embedding
+ *          output is added to the stream before every pass but the first.  Mixers: grouped-query attention over a sliding
+ *          window plus pooled blocks of what left it (TGIS_MIXER_POOLED_ATTENTION), latent attention with interleaved rotary
+ *          pairs, no window, no output gate and a sink in the softmax (TGIS_MIXER_LATENT_ATTENTION + TGIS_LAYER_* flags),
+ *          HGRN2 (TGIS_MIXER_HGRN); dense SwiGLU feed-forward (TGIS_MLP_DENSE_SILU).  bf16 or fp32 operands.  Single GPU,
+ *          no LoRA slots. */
+#define TGIS_ARCH_SIKAZEN 5
 
 /* Model + runtime configuration (bf16 decoder-only transformer; see TGIS_ARCH_*). */
 typedef struct tgis_config {
@@ -129,11 +141,21 @@ typedef struct tgis_config {
 #define TGIS_MIXER_SIGMOID_ATTENTION 5 /* grouped-query attention, rotary positions, window, weight = sigmoid(score + bias_h) */
 #define TGIS_MIXER_SSD 6             /* short convolution + per-head scalar-decay state-space scan, gated group norm */
 #define TGIS_MIXER_CHANNEL_DELTA 7   /* short convolutions + delta-rule memory whose key channels decay one by one */
+#define TGIS_MIXER_POOLED_ATTENTION 8 /* grouped-query softmax attention: rotary positions, unit-norm queries and keys, a window
+                                       * of tokens and one mean key / value for every block of `pool` tokens behind it */
+#define TGIS_MIXER_HGRN 9            /* outer-product memory whose forget gate (bounded below) also decides what is written */
 #define TGIS_MLP_NONE 0
 #define TGIS_MLP_MOE 1
 #define TGIS_MLP_DENSE_GELU 2        /* down(gelu_tanh(gate h) * (up h)), width `ff` */
 #define TGIS_MLP_MOE_SIGMOID 3       /* experts down(relu(up (s h))^2) weighted on their input by s = sigmoid(router logit), the
                                       * `top` largest, their scores used as they are; shared expert of width shared_ff added (0: none) */
+#define TGIS_MLP_DENSE_SILU 4        /* down(silu(gate h) * (up h)), width `ff` */
+/* tgis_layer_spec.flags */
+#define TGIS_LAYER_ROT_INTERLEAVED 1 /* rotary pairs are (2i, 2i + 1) instead of (i, i + rot_dims / 2) */
+#define TGIS_LAYER_SINK 2            /* the softmax denominator of head h also holds exp(sink_h): "l<i>.mix.sink" */
+#define TGIS_LAYER_NO_OUT_GATE 4     /* latent attention without the sigmoid output gate (no "l<i>.mix.g") */
+#define TGIS_LAYER_QKV_BIAS 8        /* "l<i>.mix.q.b|k.b|v.b" are added to the projections */
+#define TGIS_LAYER_UNIT_QK 16        /* queries and keys are divided by their root mean square per head after the rotation */
 typedef struct tgis_layer_spec {
   int32_t mixer;        /* TGIS_MIXER_* */
   int32_t heads, dim, rot_dim, vdim, kv_rank, q_rank; /* per head: dim unrotated + rot_dim rotated query/key dims, vdim values */
@@ -170,11 +192,20 @@ typedef struct tgis_layer_spec {
    * normed in norm_groups parts.  TGIS_MIXER_CHANNEL_DELTA: heads (values, vdim) / kv_heads (queries and keys, dim), `conv`
    * taps, decay_rank and gate_rank: inner sizes of the two low-rank maps (decay logits, output gate) */
   int32_t groups, norm_groups, gate_rank;
+  /* TGIS_MIXER_POOLED_ATTENTION: heads / kv_heads / dim / vdim / window / rot_dims / rot_base / scale as above; `pool`: tokens per
+   * pooled block (<= 0: a plain sliding window); rot_linear > 0: every rotary frequency is divided by it (also read by
+   * TGIS_MIXER_LATENT_ATTENTION).  TGIS_MIXER_HGRN: heads x dim query / gate channels, heads x vdim values.  flags: TGIS_LAYER_* */
+  int32_t pool;
+  float rot_linear;
+  int32_t flags;
+  int32_t reserved2;
 } tgis_layer_spec;
 #define TGIS_STYLE_POST_NORM 1 /* x += rmsnorm(sublayer(x)) * w with a plain weight; unset: pre- and post-norm, weights stored
                                 * as deviations from one */
 #define TGIS_STYLE_TIED_HEAD 2 /* logits = embedding table x (no "head" tensor) */
 #define TGIS_STYLE_PARALLEL_GATED 4 /* one norm per layer; x += sigmoid(R1 n + b1) * mixer(shift(n)) + sigmoid(R2 n + b2) * ff(n) */
+#define TGIS_STYLE_PARALLEL_PAIR 8  /* two norms of ONE number each; x += mixer(rms(x) g1) + ff(rms(x) g2), then the per-layer token
+                                     * input (side_dim > 0): x += rms(side.proj (gelu_tanh(side.gate x) * e)) * side.norm */
 #define TGIS_DTYPE_BF16 0 /* bf16 operands, fp32 accumulation; norms, softmax, routers and the residual sum in fp32 */
 #define TGIS_DTYPE_F32 1  /* everything in true fp32 (no TF32) */
 typedef struct tgis_model_spec {
@@ -186,6 +217,11 @@ typedef struct tgis_model_spec {
   int32_t style;        /* TGIS_STYLE_* bits */
   const tgis_layer_spec* layers; /* [n_layers] */
   float logit_scale;    /* logits = head x * logit_scale (0 is read as 1) */
+  int32_t side_dim;     /* TGIS_STYLE_PARALLEL_PAIR: columns of the side table "side.embed" [vocab, n_layers * side_dim] that layer i
+                           reads at [i * side_dim, (i + 1) * side_dim); 0: no per-layer token input */
+  /* layers [loop_start, loop_stop) run loop_times passes in a row on the same weights, every pass with cache rows and state of
+   * its own; before every pass but the first the embedding output is added to the stream.  loop_times <= 1: no loop */
+  int32_t loop_start, loop_stop, loop_times;
   int32_t reserved;
 } tgis_model_spec;
 
@@ -300,6 +336,9 @@ int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec,
  * "l<i>.mlp.router|e<j>.up|e<j>.down|shared.up|shared.down"; TGIS_MIXER_SIGMOID_ATTENTION "l<i>.mix.q|k|v|pb|o" (k, v absent
  * with kv_from); TGIS_MIXER_SSD "l<i>.mix.in|conv|conv.b|dt_bias|A_log|D|norm|o"; TGIS_MIXER_CHANNEL_DELTA "l<i>.mix.q|q.conv|k|
  * k.conv|v|v.conv|b|A_log|norm|a1|a2|dt_bias|g1|g2|o". */
+/* cfg->arch == TGIS_ARCH_SIKAZEN; parameter names: "embed", "side.embed", "head", "final.norm" (one number), "l<i>.norm1|norm2" (one
+ * number each), "l<i>.mlp.gate|up|down", "l<i>.side.gate|proj|norm"; TGIS_MIXER_POOLED_ATTENTION "l<i>.mix.q|q.b|k|k.b|v|v.b|o";
+ * TGIS_MIXER_LATENT_ATTENTION "l<i>.mix.dq|dq.norm|uq|dkv|dkv.norm|uk|uv|sink|o"; TGIS_MIXER_HGRN "l<i>.mix.q|f|f.b|lower|v|norm|o". */
 /* name: HF Llama parameter name ("model.layers.3.self_attn.q_proj.weight", "lm_head.weight", ...) or
  * "tgis.rope_cos_sin" ([max_model_len,128] bf16 = cos|sin); arch OPT: HF OPT parameter names
  * ("model.decoder.layers.3.self_attn.q_proj.bias", "model.decoder.embed_positions.weight" with >= max_model_len + 2 rows,

@@ -59,9 +59,14 @@ template <>
 __device__ __forceinline__ float widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // "rotate half" over the first rot_dims entries of a rot_dim-long vector: entry i pairs with i + rot_dims / 2
-__device__ __forceinline__ float rotary_entry(const float* v, int j, int rot_dims, const float* cs) {
+// (interleaved: entry 2i pairs with 2i + 1; the table stays cos (rot_dims / 2) | sin (rot_dims / 2))
+__device__ __forceinline__ float rotary_entry(const float* v, int j, int rot_dims, const float* cs, int interleaved = 0) {
   const int half = rot_dims / 2;
   if (j >= rot_dims) return v[j];
+  if (interleaved) {
+    const int f = j >> 1;
+    return (j & 1) ? v[j] * cs[f] + v[j - 1] * cs[half + f] : v[j] * cs[f] - v[j + 1] * cs[half + f];
+  }
   if (j < half) return v[j] * cs[j] - v[j + half] * cs[half + j];
   return v[j] * cs[j - half] + v[j - half] * cs[j];  // cs[j] with j >= half is sin(j - half)
 }
@@ -96,7 +101,7 @@ latent_prep_kernel(const float* __restrict__ y, int ldy, LatentGeom g, const flo
   for (int i = threadIdx.x; i < g.kv_rank; i += PREP_THREADS) st_any(cache, dtype, crow + i, ykv[i] * rs_kv * w_kv[i]);
   const float* cs = cos_sin + (size_t)positions[t] * g.rot_dims;
   for (int j = threadIdx.x; j < g.rot_dim; j += PREP_THREADS)
-    st_any(cache, dtype, crow + g.kv_rank + j, rotary_entry(ykr, j, g.rot_dims, cs));
+    st_any(cache, dtype, crow + g.kv_rank + j, rotary_entry(ykr, j, g.rot_dims, cs, g.interleaved));
 }
 
 template <class QT>
@@ -112,7 +117,10 @@ __global__ void latent_q_rope_kernel(const QT* __restrict__ q, LatentGeom g, con
     const QT* v = q + ((size_t)t * g.heads + h) * hd + g.dim;
     float r;  // "rotate half" over the first rot_dims entries (rotary_entry, on the stored type)
     if (j >= g.rot_dims) r = widen<QT>(v[j]);
-    else if (j < half) r = widen<QT>(v[j]) * cs[j] - widen<QT>(v[j + half]) * cs[half + j];
+    else if (g.interleaved) {
+      const int f = j >> 1;
+      r = (j & 1) ? widen<QT>(v[j]) * cs[f] + widen<QT>(v[j - 1]) * cs[half + f] : widen<QT>(v[j]) * cs[f] - widen<QT>(v[j + 1]) * cs[half + f];
+    } else if (j < half) r = widen<QT>(v[j]) * cs[j] - widen<QT>(v[j + half]) * cs[half + j];
     else r = widen<QT>(v[j]) * cs[j - half] + widen<QT>(v[j - half]) * cs[j];
     q_abs[((size_t)t * g.heads + h) * D + g.kv_rank + j] = r;
   }
@@ -212,7 +220,8 @@ latent_attn_kernel(const float* __restrict__ q_abs, const CT* __restrict__ cache
     if (!on[u]) continue;
     const int tq = pp[u] / nh, h = h0 + pp[u] % nh;
     const size_t o = ((size_t)(row0 + tq) * g.heads + h) * R;
-    const float inv = 1.f / l[u];
+    // the sink joins the denominator only: exp(sink - m) beside the keys' exp(s - m) (a causal row always sees itself: m is finite)
+    const float inv = 1.f / (l[u] + (g.sink != nullptr ? expf(g.sink[h] - m[u]) : 0.f));
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
       const int d = lane + 32 * i;
@@ -429,8 +438,9 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
     return;
   }
   if (lane == 0) {
-    if (on[0]) l_s[prow[0]] = l_run[0];
-    if (on[1]) l_s[prow[1]] = l_run[1];
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (on[u]) l_s[prow[u]] = l_run[u] + (g.sink != nullptr ? expf(g.sink[h0 + prow[u] % nh] - m_run[u]) : 0.f);
   }
   __syncthreads();
 #pragma unroll
@@ -487,6 +497,7 @@ latent_attn_merge_kernel(const float* __restrict__ part, int n_splits, const Att
       den += w * l[u];
     }
     den = warp_sum_f(den);
+    if (g.sink != nullptr) den += expf(g.sink[h0 + p % nh] - M);
     if (threadIdx.x == 0) inv_s = 1.f / den;
   }
   __syncthreads();

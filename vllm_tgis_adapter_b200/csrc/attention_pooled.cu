@@ -1,0 +1,351 @@
+// Grouped-query softmax attention over a sliding window of tokens plus pooled blocks of the tokens that left it
+// (kernels.h: PoolAttnGeom).  A query at position i sees
+//   * the tokens j with 0 <= i - j < window, each with its own key and value, and
+//   * every block b of `pool` consecutive positions with b * pool + pool - 1 <= i - window through ONE key and ONE value: the
+//     means of the block's cached keys (after rotation and norm) and values,
+// all under one softmax.  Tokens behind the window whose block is still incomplete at i - window are not seen at all.
+//
+//   poolattn_prep_kernel   per token and head: bias, rotary turn (fp32 table), unit RMS norm of queries and keys, cache write
+//   poolattn_pool_kernel   the blocks that this step's tokens complete: mean of the block's cache rows -> the pooled cache
+//   poolattn_mma_kernel    bf16 rows whose sizes fit the MMA tiles: both products on mma.sync with fp32 accumulators
+//   poolattn_kernel        any sizes and fp32 rows (FMA pipe)
+//
+// The attention kernels take one CTA per (tile of POOLATTN_TILE query tokens of one sequence, query head) and walk "chunks" of
+// 32 keys in a fixed order: first the pooled rows 0..31, 32..63, ... that the tile's last query sees, then the sequence's
+// 32-token cache blocks from the first one the tile's window touches.  Scores, the running softmax (maximum, sum) and the
+// accumulators are fp32; a key that a query does not see weighs exactly zero.  So a query row's arithmetic depends on its own
+// position and on the 32-row grids of its sequence only: not on the tile it shares with other queries, on how the prompt was cut,
+// on the other sequences of the step, or on which physical pages hold the rows.
+//
+// Pooled rows live in a cache of their own that is paged by the SAME block ids: block b belongs to the page of its first
+// token, p = b * pool / KV_BLOCK, at index b - ceil(p * KV_BLOCK / pool); a page owns ceil(KV_BLOCK / pool) of them.
+#include <cmath>
+#include <cstdint>
+#include <cstdlib>
+
+#include "kernels.h"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace tgis {
+namespace {
+
+template <class T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// pooled blocks a query at position `pos` sees
+__device__ __forceinline__ int pooled_visible(int pos, int window, int pool) {
+  const int e = pos - window + 1;   // positions [0, e) lie behind the window
+  return (window > 0 && pool > 0 && e > 0) ? e / pool : 0;
+}
+// row of pooled block b inside the pooled cache (page table bt of the sequence)
+__device__ __forceinline__ size_t pooled_row(int b, int pool, int rpp, const int32_t* bt) {
+  const int page = (int)(((long long)b * pool) / KV_BLOCK);
+  const int first = (page * KV_BLOCK + pool - 1) / pool;   // first block whose first token lies in the page
+  return (size_t)bt[page] * rpp + (b - first);
+}
+
+// ---------------------------------------------------------------------------------------------------------------- prep
+// grid (T, ceil((heads + 2 kv_heads) / 4)), 128 threads: one warp per (token, query head | key head | value head)
+constexpr int PREP_WARPS = 4, PREP_MAX = 16;   // dim <= 32 * PREP_MAX
+template <class CT>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+poolattn_prep_kernel(const float* __restrict__ y, int ldy, int q_off, int k_off, int v_off, const float* __restrict__ bias,
+                     PoolAttnGeom g, const float* __restrict__ cos_sin, float eps, const int32_t* __restrict__ positions,
+                     const int32_t* __restrict__ slot_mapping, CT* __restrict__ q_out, CT* __restrict__ k_cache,
+                     CT* __restrict__ v_cache) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x, hh = blockIdx.y * PREP_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (hh >= g.heads + 2 * g.kv_heads) return;
+  const int slot = slot_mapping[t];
+  const int nq = g.heads * g.dim, nk = g.kv_heads * g.dim;
+  if (hh < g.heads + g.kv_heads) {
+    const bool is_q = hh < g.heads;
+    const int h = is_q ? hh : hh - g.heads;
+    if (!is_q && slot < 0) return;
+    const float* src = y + (size_t)t * ldy + (is_q ? q_off : k_off) + (size_t)h * g.dim;
+    const float* b = bias != nullptr ? bias + (is_q ? 0 : nq) + (size_t)h * g.dim : nullptr;
+    const float* cs = cos_sin != nullptr ? cos_sin + (size_t)positions[t] * g.rot_dims : nullptr;
+    const int half = g.rot_dims / 2;
+    float val[PREP_MAX];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < PREP_MAX; ++e) {
+      const int i = lane + 32 * e;
+      float v = 0.f;
+      if (i < g.dim) {
+        v = src[i] + (b ? b[i] : 0.f);
+        if (i < g.rot_dims) {
+          const int j = i < half ? i + half : i - half, f = i < half ? i : i - half;
+          const float w = src[j] + (b ? b[j] : 0.f);
+          v = i < half ? v * cs[f] - w * cs[half + f] : v * cs[f] + w * cs[half + f];
+        }
+      }
+      val[e] = v;
+      ss = fmaf(v, v, ss);
+    }
+    const float rs = g.unit_norm ? 1.f / sqrtf(warp_sum_f(ss) / (float)g.dim + eps) : 1.f;
+    CT* dst = is_q ? q_out + ((size_t)t * g.heads + h) * g.dim : k_cache + ((size_t)slot * g.kv_heads + h) * g.dim;
+#pragma unroll
+    for (int e = 0; e < PREP_MAX; ++e) {
+      const int i = lane + 32 * e;
+      if (i < g.dim) stf(dst + i, val[e] * rs);
+    }
+  } else if (slot >= 0) {
+    const int h = hh - g.heads - g.kv_heads;
+    const float* src = y + (size_t)t * ldy + v_off + (size_t)h * g.vdim;
+    const float* b = bias != nullptr ? bias + nq + nk + (size_t)h * g.vdim : nullptr;
+    CT* dst = v_cache + ((size_t)slot * g.kv_heads + h) * g.vdim;
+    for (int i = lane; i < g.vdim; i += 32) stf(dst + i, src[i] + (b ? b[i] : 0.f));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- pool
+// grid (sequences, blocks per sequence in strides of gridDim.y), 128 threads over the columns of a K | V row
+template <class CT>
+__global__ void __launch_bounds__(128)
+poolattn_pool_kernel(const CT* __restrict__ k_cache, const CT* __restrict__ v_cache, CT* __restrict__ pk, CT* __restrict__ pv,
+                     const AttnSeq* __restrict__ seqs, const int32_t* __restrict__ block_table, int bt_stride, PoolAttnGeom g) {
+  griddep_launch();
+  griddep_wait();
+  const AttnSeq sq = seqs[blockIdx.x];
+  const int P = g.pool, first = sq.kv_len - sq.q_len;
+  const int b_lo = first / P, b_hi = sq.kv_len / P;   // blocks whose last position is one of this step's tokens
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  const int nk = g.kv_heads * g.dim, nv = g.kv_heads * g.vdim, rpp = g.rows_per_page();
+  const float inv = 1.f / (float)P;
+  for (int b = b_lo + blockIdx.y; b < b_hi; b += gridDim.y) {
+    const size_t dst = pooled_row(b, P, rpp, bt);
+    for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
+      float s = 0.f;
+      for (int r = 0; r < P; ++r) {   // position order
+        const int pos = b * P + r;
+        const size_t row = (size_t)bt[pos / KV_BLOCK] * KV_BLOCK + pos % KV_BLOCK;
+        s += c < nk ? ldf(k_cache + row * nk + c) : ldf(v_cache + row * nv + (c - nk));
+      }
+      if (c < nk) stf(pk + dst * nk + c, s * inv);
+      else stf(pv + dst * nv + (c - nk), s * inv);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------- FMA kernel
+constexpr int PA_THREADS = 128, PA_QT = POOLATTN_TILE, PA_CC = POOLATTN_MAX_VDIM / PA_THREADS;
+static_assert(PA_QT == 16 && PA_THREADS == 128, "score mapping: 4 warps x 4 queries x 32 keys");
+
+template <class CT, class OT>
+__global__ void __launch_bounds__(PA_THREADS)
+poolattn_kernel(const CT* __restrict__ q, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
+                const CT* __restrict__ pk, const CT* __restrict__ pv, const AttnSeq* __restrict__ seqs,
+                const LatentTile* __restrict__ tiles, const int32_t* __restrict__ block_table, int bt_stride,
+                OT* __restrict__ out, PoolAttnGeom g) {
+  extern __shared__ __align__(16) float pa_smem[];
+  const int d = g.dim, dv = g.vdim, ldk = d + 1;
+  float* Qs = pa_smem;                        // [PA_QT][d]      scaled queries
+  float* Ks = Qs + PA_QT * d;                 // [KV_BLOCK][d+1]
+  float* Vs = Ks + KV_BLOCK * ldk;            // [KV_BLOCK][dv]
+  float* Ps = Vs + KV_BLOCK * dv;             // [PA_QT][KV_BLOCK]
+  float* alpha = Ps + PA_QT * KV_BLOCK;       // [PA_QT]
+  float* lsum = alpha + PA_QT;                // [PA_QT]
+  __shared__ long long rowoff[KV_BLOCK];      // cache row of every key of the chunk (-1: none)
+  griddep_launch();
+  griddep_wait();
+  const LatentTile tl = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tl.seq];
+  const int h = blockIdx.y, kvh = h / (g.heads / g.kv_heads);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = sq.q_start + tl.q0;             // first query row of the tile in the flat batch
+  const int pos0 = sq.kv_len - sq.q_len + tl.q0;   // its position
+  const int nq = tl.nq, pos_last = pos0 + nq - 1;
+  for (int i = tid; i < PA_QT * d; i += PA_THREADS) {
+    const int qi = i / d, kk = i % d;
+    Qs[i] = qi < nq ? ldf(q + ((size_t)(row0 + qi) * g.heads + h) * d + kk) * g.scale : 0.f;
+  }
+  float acc[PA_QT][PA_CC];
+#pragma unroll
+  for (int qi = 0; qi < PA_QT; ++qi)
+#pragma unroll
+    for (int cc = 0; cc < PA_CC; ++cc) acc[qi][cc] = 0.f;
+  float m_run[4], l_run[4];   // this warp's four query rows (valid in every lane)
+  int n_vis[4];               // pooled blocks each of them sees
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -INFINITY;
+    l_run[i] = 0.f;
+    n_vis[i] = pooled_visible(pos0 + warp * 4 + i, g.window, g.pool);
+  }
+  const int n_pooled = pooled_visible(pos_last, g.window, g.pool);
+  const int n_pc = (n_pooled + KV_BLOCK - 1) / KV_BLOCK;
+  const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
+  const int blk0 = kmin / KV_BLOCK, blk1 = pos_last / KV_BLOCK;
+  const int n_chunks = n_pc + blk1 - blk0 + 1;
+  const int rpp = g.rows_per_page();
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  for (int c = 0; c < n_chunks; ++c) {
+    const bool pooled = c < n_pc;
+    __syncthreads();   // the previous chunk's Ks / Vs / Ps / rowoff are consumed (first pass: Qs complete)
+    if (tid < KV_BLOCK) {
+      long long r;
+      if (pooled) {
+        const int b = c * KV_BLOCK + tid;
+        r = b < n_pooled ? (long long)pooled_row(b, g.pool, rpp, bt) : -1;
+      } else {
+        r = (long long)bt[blk0 + c - n_pc] * KV_BLOCK + tid;
+      }
+      rowoff[tid] = r;
+    }
+    __syncthreads();
+    const CT* kb = pooled ? pk : k_cache;
+    const CT* vb = pooled ? pv : v_cache;
+    for (int i = tid; i < KV_BLOCK * d; i += PA_THREADS) {
+      const int j = i / d, kk = i % d;
+      const long long r = rowoff[j];
+      Ks[j * ldk + kk] = r >= 0 ? ldf(kb + ((size_t)r * g.kv_heads + kvh) * d + kk) : 0.f;
+    }
+    for (int i = tid; i < KV_BLOCK * dv; i += PA_THREADS) {
+      const int j = i / dv, cc = i % dv;
+      const long long r = rowoff[j];
+      Vs[i] = r >= 0 ? ldf(vb + ((size_t)r * g.kv_heads + kvh) * dv + cc) : 0.f;
+    }
+    __syncthreads();
+    // ---- scores: lane = key, this warp's four queries
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* kr = Ks + lane * ldk;
+    const float* qr = Qs + warp * 4 * d;
+    for (int kk = 0; kk < d; ++kk) {
+      const float kv = kr[kk];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[i] = fmaf(qr[i * d + kk], kv, s[i]);
+    }
+    const int kidx = (pooled ? c : blk0 + c - n_pc) * KV_BLOCK + lane;   // pooled block number, or token position
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qi = warp * 4 + i, pi = pos0 + qi;
+      const bool ok = qi < nq && (pooled ? kidx < n_vis[i] : (kidx <= pi && (g.window <= 0 || pi - kidx < g.window)));
+      const float sc = ok ? s[i] : -INFINITY;
+      const float m_new = fmaxf(m_run[i], warp_max_f(sc));
+      const float p = ok ? expf(sc - m_new) : 0.f;
+      const float al = m_new == -INFINITY ? 1.f : expf(m_run[i] - m_new);   // (-inf: nothing seen yet, nothing to scale)
+      l_run[i] = fmaf(l_run[i], al, warp_sum_f(p));
+      m_run[i] = m_new;
+      Ps[qi * KV_BLOCK + lane] = p;
+      if (lane == 0) alpha[qi] = al;
+    }
+    __syncthreads();
+    // ---- weighted sum of the values: thread = value column(s), all queries of the tile
+#pragma unroll
+    for (int cc = 0; cc < PA_CC; ++cc) {
+      const int col = tid + cc * PA_THREADS;
+      if (col < dv) {
+#pragma unroll
+        for (int qi = 0; qi < PA_QT; ++qi)
+          if (qi < nq) acc[qi][cc] *= alpha[qi];
+        for (int j = 0; j < KV_BLOCK; ++j) {
+          const float vv = Vs[j * dv + col];
+#pragma unroll
+          for (int qi = 0; qi < PA_QT; ++qi)
+            if (qi < nq) acc[qi][cc] = fmaf(Ps[qi * KV_BLOCK + j], vv, acc[qi][cc]);
+        }
+      }
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) lsum[warp * 4 + i] = l_run[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int cc = 0; cc < PA_CC; ++cc) {
+    const int col = tid + cc * PA_THREADS;
+    if (col < dv) {
+#pragma unroll
+      for (int qi = 0; qi < PA_QT; ++qi)
+        if (qi < nq) stf(out + ((size_t)(row0 + qi) * g.heads + h) * dv + col, acc[qi][cc] / lsum[qi]);
+    }
+  }
+}
+
+template <class CT>
+cudaError_t launch_fma(const void* q, const void* k_cache, const void* v_cache, const void* pk, const void* pv,
+                       const AttnSeq* seqs, const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
+                       void* out, const PoolAttnGeom& g, cudaStream_t stream) {
+  const size_t smem = ((size_t)PA_QT * g.dim + (size_t)KV_BLOCK * (g.dim + 1) + (size_t)KV_BLOCK * g.vdim + PA_QT * KV_BLOCK +
+                       2 * PA_QT) * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidValue;
+  static size_t attr_bytes = 0;   // per instantiation
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    const cudaError_t e = cudaFuncSetAttribute(poolattn_kernel<CT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    attr_bytes = smem;
+  }
+  return launch_k(poolattn_kernel<CT, CT>, dim3(n_tiles, g.heads), dim3(PA_THREADS), smem, stream,
+                  reinterpret_cast<const CT*>(q), reinterpret_cast<const CT*>(k_cache), reinterpret_cast<const CT*>(v_cache),
+                  reinterpret_cast<const CT*>(pk), reinterpret_cast<const CT*>(pv), seqs, tiles, block_table, bt_stride,
+                  reinterpret_cast<CT*>(out), g);
+}
+
+bool geom_ok(const PoolAttnGeom& g) {
+  return g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0 && g.heads <= 65535 && g.dim >= 1 && g.vdim >= 1 &&
+         g.dim <= 32 * PREP_MAX && g.vdim <= POOLATTN_MAX_VDIM && g.rot_dims >= 0 && g.rot_dims <= g.dim && (g.rot_dims & 1) == 0;
+}
+
+}  // namespace
+
+cudaError_t poolattn_prep_launch(const float* y, int ldy, int q_off, int k_off, int v_off, const float* bias,
+                                 const PoolAttnGeom& g, const float* cos_sin, float eps, const int32_t* positions,
+                                 const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
+                                 cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  if (!geom_ok(g) || (g.rot_dims > 0 && cos_sin == nullptr)) return cudaErrorInvalidValue;
+  const dim3 grid(T, (g.heads + 2 * g.kv_heads + PREP_WARPS - 1) / PREP_WARPS);
+  if (dtype == DT_BF16)
+    return launch_k(poolattn_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, bias,
+                    g, cos_sin, eps, positions, slot_mapping, reinterpret_cast<__nv_bfloat16*>(q_out),
+                    reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache));
+  return launch_k(poolattn_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, bias, g, cos_sin,
+                  eps, positions, slot_mapping, reinterpret_cast<float*>(q_out), reinterpret_cast<float*>(k_cache),
+                  reinterpret_cast<float*>(v_cache));
+}
+
+cudaError_t poolattn_pool_launch(const void* k_cache, const void* v_cache, void* pk, void* pv, int dtype,
+                                 const AttnSeq* seqs, int n_seqs, const int32_t* block_table, int bt_stride,
+                                 const PoolAttnGeom& g, int max_q_len, cudaStream_t stream) {
+  if (n_seqs <= 0 || g.pool <= 0 || g.window <= 0) return cudaSuccess;
+  if (!geom_ok(g)) return cudaErrorInvalidValue;
+  const dim3 grid(n_seqs, std::min(max_q_len / g.pool + 1, 4096));
+  if (dtype == DT_BF16)
+    return launch_k(poolattn_pool_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream,
+                    reinterpret_cast<const __nv_bfloat16*>(k_cache), reinterpret_cast<const __nv_bfloat16*>(v_cache),
+                    reinterpret_cast<__nv_bfloat16*>(pk), reinterpret_cast<__nv_bfloat16*>(pv), seqs, block_table, bt_stride, g);
+  return launch_k(poolattn_pool_kernel<float>, grid, dim3(128), 0, stream, reinterpret_cast<const float*>(k_cache),
+                  reinterpret_cast<const float*>(v_cache), reinterpret_cast<float*>(pk), reinterpret_cast<float*>(pv), seqs,
+                  block_table, bt_stride, g);
+}
+
+cudaError_t poolattn_launch(const void* q, const void* k_cache, const void* v_cache, const void* pk, const void* pv, int dtype,
+                            const AttnSeq* seqs, const LatentTile* tiles, int n_tiles, const int32_t* block_table,
+                            int bt_stride, void* out, int out_dtype, const PoolAttnGeom& g, cudaStream_t stream) {
+  if (n_tiles <= 0) return cudaSuccess;
+  if (!geom_ok(g) || out_dtype != dtype) return cudaErrorInvalidValue;
+  if (dtype == DT_BF16)
+    return launch_fma<__nv_bfloat16>(q, k_cache, v_cache, pk, pv, seqs, tiles, n_tiles, block_table, bt_stride, out, g, stream);
+  return launch_fma<float>(q, k_cache, v_cache, pk, pv, seqs, tiles, n_tiles, block_table, bt_stride, out, g, stream);
+}
+
+}  // namespace tgis

@@ -757,8 +757,14 @@ __global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, i
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
       r.v[e] = x.v[e] + a.mult * (y.v[e] * rs * (a.w_off + w.v[e]));
-      ss2 += r.v[e] * r.v[e];
     }
+    if (a.extra != nullptr) {
+      const FV<VEC> ex = ld_fv<VEC>(a.extra + base + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) r.v[e] += ex.v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ss2 += r.v[e] * r.v[e];
     st_fv<VEC>(a.resid + base + i, r);
     st_fv<VEC>(row_buf + i, r);
   }
@@ -783,6 +789,11 @@ __global__ void __launch_bounds__(NORM_THREADS) resid_tail_kernel(ResidTail a, i
 #pragma unroll
       for (int e = 0; e < VEC; ++e) st_dt(a.out, a.out_dtype, base + i + e, r.v[e] * rs2 * (a.w_off + w.v[e]));
     }
+    if (a.w_pre2 != nullptr) {
+      const FV<VEC> w2 = ld_fv<VEC>(a.w_pre2 + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st_dt(a.out2, a.out_dtype, base + i + e, r.v[e] * rs2 * (a.w_off + w2.v[e]));
+    }
   }
 }
 cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream) {
@@ -790,7 +801,8 @@ cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_
   if (a.w_post == nullptr || a.resid == nullptr || (size_t)hidden * 4 > 48 * 1024) return cudaErrorInvalidValue;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   if (a.y_pair != nullptr && (a.y_main == nullptr || a.w_main == nullptr || a.w_pair == nullptr)) return cudaErrorInvalidValue;
-  const bool vec = hidden % 4 == 0 && al16(a.y_main) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_post) &&
+  if (a.w_pre2 != nullptr && (a.w_pre == nullptr || a.out2 == nullptr)) return cudaErrorInvalidValue;
+  const bool vec = hidden % 4 == 0 && al16(a.extra) && al16(a.w_pre2) && al16(a.out2) && al16(a.y_main) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_post) &&
                    al16(a.w_pre) && al16(a.out) && al16(a.y_pair) && al16(a.w_main) && al16(a.w_pair);
   if (vec) return launch_k(resid_tail_kernel<4>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
   return launch_k(resid_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden);
@@ -834,11 +846,22 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_tail_kernel(GatedTail a, i
         upd = fmaf(g2, f.v[e], upd);
       }
       r.v[e] = x.v[e] + upd;
-      ss = fmaf(r.v[e], r.v[e], ss);
     }
+    if (a.extra != nullptr) {
+      const FV<VEC> ex = ld_fv<VEC>(a.extra + base + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) r.v[e] += ex.v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ss = fmaf(r.v[e], r.v[e], ss);
     st_fv<VEC>(a.resid + base + i, r);
     st_fv<VEC>(row_buf + i, r);
+    if (a.resid_out != nullptr) {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st_dt(a.resid_out, a.out_dtype, base + i + e, r.v[e]);
+    }
   }
+  if (a.w_next == nullptr) return;   // the stream itself is what the next step reads
   // the token shift's state of this layer: the normed row its last token of the portion was given
   if (a.prev_state != nullptr && (t + 1 == T || a.tok_slot[t + 1] != a.tok_slot[t])) {
     float* dst = a.prev_state + (size_t)a.tok_slot[t] * hidden;
@@ -855,15 +878,21 @@ __global__ void __launch_bounds__(NORM_THREADS) gated_tail_kernel(GatedTail a, i
 #pragma unroll
       for (int e = 0; e < VEC; ++e) st_dt(a.out, a.out_dtype, base + i + e, n.v[e]);
     }
+    if (a.w_next2 != nullptr) {
+      const FV<VEC> w2 = ld_fv<VEC>(a.w_next2 + i);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) st_dt(a.out2, a.out_dtype, base + i + e, r.v[e] * rs * w2.v[e] * a.out_scale);
+    }
   }
 }
 cudaError_t gated_tail_launch(const GatedTail& a, int T, int hidden, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  if (a.y_mix == nullptr || a.resid == nullptr || a.w_next == nullptr || (size_t)hidden * 4 > 48 * 1024 ||
+  if (a.y_mix == nullptr || a.resid == nullptr || (a.w_next == nullptr && a.resid_out == nullptr) || (size_t)hidden * 4 > 48 * 1024 ||
+      (a.w_next2 != nullptr && (a.out2 == nullptr || a.w_next == nullptr)) ||
       (a.gl != nullptr && (a.b1 == nullptr || a.b2 == nullptr)) || (a.prev_state != nullptr && (a.n_cur == nullptr || a.tok_slot == nullptr)))
     return cudaErrorInvalidValue;
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  const bool vec = hidden % 4 == 0 && al16(a.y_mix) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_next) &&
+  const bool vec = hidden % 4 == 0 && al16(a.extra) && al16(a.w_next2) && al16(a.y_mix) && al16(a.y_rows) && al16(a.y_side) && al16(a.resid) && al16(a.w_next) &&
                    al16(a.n_f32) && al16(a.n_cur) && al16(a.prev_state);
   if (vec) return launch_k(gated_tail_kernel<4>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden, T);
   return launch_k(gated_tail_kernel<1>, dim3(T), dim3(NORM_THREADS), (size_t)hidden * sizeof(float), stream, a, hidden, T);
@@ -881,6 +910,29 @@ __global__ void gather_rows_any_kernel(const int32_t* __restrict__ idx, const ui
   else
     for (int i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
 }
+// grid (T), 128 threads: a gate on the token's slice of a side table
+__global__ void __launch_bounds__(128)
+gelu_gate_rows_kernel(const float* __restrict__ z, int ldz, const int32_t* __restrict__ token_ids, const void* __restrict__ table,
+                      int table_dtype, int ld_table, int col0, int n, void* __restrict__ out, int out_dtype) {
+  griddep_launch();
+  griddep_wait();
+  const int t = blockIdx.x;
+  const size_t trow = (size_t)token_ids[t] * ld_table + col0;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float g = z[(size_t)t * ldz + j];
+    const float e = table_dtype == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(table)[trow + j])
+                                           : reinterpret_cast<const float*>(table)[trow + j];
+    const float act = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    st_dt(out, out_dtype, (size_t)t * n + j, act * e);
+  }
+}
+cudaError_t gelu_gate_rows_launch(const float* z, int ldz, const int32_t* token_ids, const void* table, int table_dtype,
+                                  int ld_table, int col0, int n, void* out, int out_dtype, int T, cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return cudaSuccess;
+  return launch_k(gelu_gate_rows_kernel, dim3(T), dim3(128), 0, stream, z, ldz, token_ids, table, table_dtype, ld_table, col0, n,
+                  out, out_dtype);
+}
+
 cudaError_t gather_rows_any_launch(const void* x, const int32_t* rows, void* out, int R, int hidden, int dtype,
                                    cudaStream_t stream) {
   if (R <= 0) return cudaSuccess;

@@ -247,7 +247,7 @@ struct tgis_engine {
     void* cache = nullptr;           // [num_blocks][KV_BLOCK][kv_rank + rot_dim], operand type
     void *w_router = nullptr, *w_gu_e = nullptr, *w_d_e = nullptr, *w_gu_s = nullptr, *w_d_s = nullptr;
     float* router_b = nullptr;
-    int n_down() const { return sp.q_rank + sp.kv_rank + sp.rot_dim + sp.heads; }
+    int n_down() const { return sp.q_rank + sp.kv_rank + sp.rot_dim + (out_gate ? sp.heads : 0); }
     // ---- mixers with state slots and the dense feed-forward (TGIS_ARCH_FALERAX)
     void* w_in = nullptr;             // every projection that reads the mixer input, stacked ([in_cols, width], operand type)
     int in_cols = 0;                  // ... rounded up to a multiple of 8 (zero rows)
@@ -277,7 +277,25 @@ struct tgis_engine {
     // TGIS_MIXER_SSD (w_in as stored: z | x | B | C | dt) and TGIS_MIXER_CHANNEL_DELTA (w_in: q | k | v | beta | decay rank | gate rank)
     int conv_ch = 0, c_b = 0, c_a1 = 0, c_g1 = 0;
     void* w_g2 = nullptr;             // channel delta: output-gate up-projection (w_w2: the decay's)
+    // ---- layers of the parallel pair style (TGIS_ARCH_SIKAZEN): two one-number norms (kept as rows of `width` equal entries),
+    // mixer and dense feed-forward side by side, then the per-layer token input
+    PoolAttnGeom pa{};                // TGIS_MIXER_POOLED_ATTENTION (w_in: q | k | v; k_cache / v_cache as above)
+    void *pk_cache = nullptr, *pv_cache = nullptr;   // pooled rows [num_blocks][rows_per_page][kv_heads * dim | vdim], operand type
+    float *in_bias = nullptr, *sink = nullptr;       // [in_cols] projection biases; [heads] softmax sinks
+    bool out_gate = true;             // latent attention: sigmoid output gate per head (its logits ride in w_down)
+    void *w_sg = nullptr, *w_sp = nullptr;           // token input: gate [side_dim, width], projection [width, side_dim]
+    float* side_norm = nullptr;
+    int weights_of = -1;              // the layer of the checkpoint whose weights this run uses
+    bool add_x0 = false;              // the embedding output is added to the stream right before this run
+    int c_f = 0;                      // TGIS_MIXER_HGRN (w_in: q | f | v): column of the gate logits
   };
+  std::vector<PnxLayer> pair_runs;    // parallel pair style: one entry per layer RUN (a looped span repeats), weights shared
+  bool pair_style = false;            // TGIS_STYLE_PARALLEL_PAIR
+  void *pnx_side = nullptr, *pnx_hB = nullptr;       // side table [vocab, n_layers * side_dim]; norm2's rows (operand type)
+  float* pnx_x0 = nullptr;                           // the embedding output, kept for the passes of a loop
+  int step_max_q = 0;                                // longest portion of the step
+  size_t off_ltiles16 = 0;                           // query tiles of POOLATTN_TILE tokens (the latent attention's are smaller)
+  int step_n_ltiles16 = 0;
   std::vector<PnxLayer> pnx_layers;
   std::vector<void*> pnx_allocs;                     // everything pnx_alloc handed out
   std::vector<std::pair<std::vector<float>, float*>> pnx_rope_tables;  // (base, dims, scaling) -> table
@@ -498,7 +516,7 @@ struct tgis_engine {
     Fl = c.ffn / tp;
     Vl = c.vocab / tp;
     opt = c.arch == TGIS_ARCH_OPT;
-    pnx_on = c.arch == TGIS_ARCH_PONENEX || c.arch == TGIS_ARCH_FALERAX || c.arch == TGIS_ARCH_REVEPEL;  // the layer-list architectures
+    pnx_on = c.arch == TGIS_ARCH_PONENEX || c.arch == TGIS_ARCH_FALERAX || c.arch == TGIS_ARCH_REVEPEL || c.arch == TGIS_ARCH_SIKAZEN;  // the layer-list architectures
     if (pnx_on) logits_bf16 = false;  // fp32 logits straight from the accumulators
     model_head_dim = opt ? c.head_dim : HEAD_DIM;
     attn_scale = 1.0f / std::sqrt((float)model_head_dim);  // zero-padded head dims add nothing to q . k
@@ -673,6 +691,7 @@ struct tgis_engine {
     off_epoch = place(4 * sizeof(uint32_t));  // tensor parallelism: exchange epochs before this step ([0], [1]: per
                                                // parity) and the logits-gather epoch ([2])
     off_ltiles = place(sizeof(LatentTile) * (size_t)(T_max + S_max));  // attention query tiles of the layer-list architectures
+    off_ltiles16 = place(sizeof(LatentTile) * (size_t)(T_max / POOLATTN_TILE + S_max + 1));
     off_bt = place(4 * (size_t)S_max * bt_stride);
     // decode work items follow the USED part of the block table (items_off(S)); room for the worst case
     place(sizeof(DecItem) * (1 + (size_t)S_max * max_splits_cap));
@@ -1185,14 +1204,16 @@ struct tgis_engine {
   // YaRN scaling (factor > 0): with dim(t) = dims ln(original / (2 pi t)) / (2 ln base) the dimension whose wave makes t turns
   // over `original` positions, lo = max(floor(dim(fast)), 0), hi = min(ceil(dim(slow)), dims - 1) and the ramp
   // r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1):  f_i <- f_i / factor * r_i + f_i (1 - r_i), cos and sin times 0.1 ln(factor) + 1.
-  const float* pnx_rope_table(float base, int dims, float factor = 0.f, float original = 0.f, float fast = 0.f, float slow = 0.f) {
-    const std::vector<float> key = {base, (float)dims, factor, original, fast, slow};
+  // linear > 0: every frequency is divided by it (linear position scaling).
+  const float* pnx_rope_table(float base, int dims, float factor = 0.f, float original = 0.f, float fast = 0.f, float slow = 0.f,
+                              float linear = 1.f) {
+    const std::vector<float> key = {base, (float)dims, factor, original, fast, slow, linear};
     for (auto& kv : pnx_rope_tables)
       if (kv.first == key) return kv.second;
     const int half = dims / 2;
     std::vector<double> freq(std::max(half, 1));
     double mag = 1.0;
-    for (int i = 0; i < half; ++i) freq[i] = std::pow((double)base, -2.0 * i / dims);
+    for (int i = 0; i < half; ++i) freq[i] = std::pow((double)base, -2.0 * i / dims) / (linear > 0.f ? (double)linear : 1.0);
     if (factor > 0.f) {
       const double pi = 3.14159265358979323846;
       auto turn_dim = [&](double turns) { return dims * std::log((double)original / (2.0 * pi * turns)) / (2.0 * std::log((double)base)); };
@@ -1226,6 +1247,7 @@ struct tgis_engine {
     post_norm = (pnx_spec.style & TGIS_STYLE_POST_NORM) != 0;
     tied_head = (pnx_spec.style & TGIS_STYLE_TIED_HEAD) != 0;
     gated_style = (pnx_spec.style & TGIS_STYLE_PARALLEL_GATED) != 0;
+    pair_style = (pnx_spec.style & TGIS_STYLE_PARALLEL_PAIR) != 0;
     pnx_embed = pnx_alloc_dt(V * W);
     pnx_head = tied_head ? pnx_embed : pnx_alloc_dt(V * W);
     pnx_final_norm = pnx_alloc<float>(W);
@@ -1239,6 +1261,83 @@ struct tgis_engine {
       PnxLayer& l = pnx_layers[i];
       const tgis_layer_spec& s = pnx_layer_specs[i];
       l.sp = s;
+      if (pair_style) {   // weights only: cache rows and state belong to the layer RUNS (pair_runs, below)
+        const size_t sd = pnx_spec.side_dim;
+        l.weights_of = (int)i;
+        l.norm1 = pnx_alloc<float>(W);
+        pnx_expected_tensors += 1;
+        if (s.mlp == TGIS_MLP_DENSE_SILU) {
+          l.norm2 = pnx_alloc<float>(W);
+          l.w_gu = pnx_alloc_dt((size_t)2 * s.ff * W);
+          l.w_d = pnx_alloc_dt(W * s.ff);
+          pnx_expected_tensors += 4;  // norm2, mlp.gate, mlp.up, mlp.down
+          m_ffs = std::max<size_t>(m_ffs, s.ff);
+        }
+        if (sd > 0) {
+          l.w_sg = pnx_alloc_dt(sd * W);
+          l.w_sp = pnx_alloc_dt(W * sd);
+          l.side_norm = pnx_alloc<float>(W);
+          pnx_expected_tensors += 3;  // side.gate, side.proj, side.norm
+          m_E = std::max(m_E, sd); m_qr = std::max(m_qr, sd);
+        }
+        m_mix = std::max(m_mix, W);
+        const float lin = s.rot_linear > 0.f ? s.rot_linear : 1.f;
+        if (s.mixer == TGIS_MIXER_POOLED_ATTENTION) {
+          const int H = s.heads, G = s.kv_heads;
+          l.pa = PoolAttnGeom{H, G, s.dim, s.vdim, s.window, s.window > 0 ? s.pool : 0, s.rot_dims, s.scale,
+                              (s.flags & TGIS_LAYER_UNIT_QK) != 0 ? 1 : 0};
+          l.c_q = 0; l.c_k = H * s.dim; l.c_v = l.c_k + G * s.dim;
+          l.in_cols = (l.c_v + G * s.vdim + 7) / 8 * 8;
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_o = pnx_alloc_dt(W * H * s.vdim);
+          if ((s.flags & TGIS_LAYER_QKV_BIAS) != 0) {
+            l.in_bias = pnx_alloc<float>(l.in_cols, true);
+            pnx_expected_tensors += 3;  // q.b, k.b, v.b
+          }
+          l.cos_sin = s.rot_dims > 0 ? pnx_rope_table(s.rot_base, s.rot_dims, 0.f, 0.f, 0.f, 0.f, lin) : nullptr;
+          pnx_expected_tensors += 4;  // q, k, v, o
+          m_q = std::max<size_t>(m_q, (size_t)H * s.dim);
+          m_ov = std::max<size_t>(m_ov, (size_t)H * s.vdim);
+          m_down = std::max<size_t>(m_down, l.in_cols);
+        } else if (s.mixer == TGIS_MIXER_HGRN) {
+          const size_t H = s.heads, hd = H * s.dim, hv = H * s.vdim;
+          l.c_q = 0; l.c_f = (int)hd; l.c_v = (int)(2 * hd);
+          l.in_cols = (int)((2 * hd + hv + 7) / 8 * 8);
+          l.w_in = pnx_alloc_dt((size_t)l.in_cols * W, true);
+          l.w_o = pnx_alloc_dt(W * hv);
+          l.w0 = pnx_alloc<float>(hd);        // the gate's bias
+          l.u = pnx_alloc<float>(hd);         // its lower bound
+          l.mm_norm = pnx_alloc<float>(hv);   // the per-head weight, repeated for every head
+          pnx_expected_tensors += 7;  // q, f, f.b, lower, v, norm, o
+          m_f1 = std::max(m_f1, hv);
+          m_down = std::max<size_t>(m_down, l.in_cols);
+        } else {  // TGIS_MIXER_LATENT_ATTENTION
+          l.out_gate = (s.flags & TGIS_LAYER_NO_OUT_GATE) == 0;
+          l.g = LatentGeom{s.heads, s.dim, s.rot_dim, s.vdim, s.kv_rank, s.q_rank, s.window, s.rot_dims, s.scale,
+                           (s.flags & TGIS_LAYER_ROT_INTERLEAVED) != 0 ? 1 : 0, nullptr};
+          const size_t hd = (size_t)s.dim + s.rot_dim, row = (size_t)s.kv_rank + s.rot_dim;
+          l.w_down = pnx_alloc_dt((size_t)l.n_down() * W);
+          l.w_uq = pnx_alloc_dt((size_t)s.heads * hd * s.q_rank);
+          l.w_ukT = pnx_alloc_dt((size_t)s.heads * s.kv_rank * s.dim);
+          l.w_uv = pnx_alloc_dt((size_t)s.heads * s.vdim * s.kv_rank);
+          l.w_o = pnx_alloc_dt(W * s.heads * s.vdim);
+          l.qnorm = pnx_alloc<float>(s.q_rank);
+          l.kvnorm = pnx_alloc<float>(s.kv_rank);
+          if ((s.flags & TGIS_LAYER_SINK) != 0) {
+            l.sink = pnx_alloc<float>(s.heads);
+            l.g.sink = l.sink;
+            pnx_expected_tensors += 1;
+          }
+          l.cos_sin = pnx_rope_table(s.rot_base, s.rot_dims, 0.f, 0.f, 0.f, 0.f, lin);
+          pnx_expected_tensors += 8 + (l.out_gate ? 1 : 0);  // dq, dq.norm, uq, dkv, dkv.norm, uk, uv, o (+ g)
+          m_down = std::max<size_t>(m_down, l.n_down()); m_qr = std::max<size_t>(m_qr, s.q_rank);
+          m_q = std::max(m_q, s.heads * hd); m_qabs = std::max(m_qabs, s.heads * row);
+          m_olat = std::max(m_olat, (size_t)s.heads * s.kv_rank); m_ov = std::max(m_ov, (size_t)s.heads * s.vdim);
+          m_heads = std::max<size_t>(m_heads, s.heads);
+          pnx_tile_tokens = std::min(pnx_tile_tokens, latent_tile_tokens(s.heads));
+        }
+        continue;
+      }
       if (gated_style) {
         const size_t slots = S_max, E = s.mlp == TGIS_MLP_MOE_SIGMOID ? s.experts : 0;
         l.norm1 = pnx_alloc<float>(W);
@@ -1424,6 +1523,36 @@ struct tgis_engine {
       cache_row_bytes += row * dt_size(pnx_dt);
       pnx_tile_tokens = std::min(pnx_tile_tokens, latent_tile_tokens(s.heads));
     }
+    if (pair_style) {
+      // the layer runs: layers [loop_start, loop_stop) repeat loop_times passes in a row; every run owns cache rows and state
+      const int L = (int)pnx_layers.size(), a = pnx_spec.loop_start, b = pnx_spec.loop_stop;
+      const int passes = (pnx_spec.loop_times > 1 && b > a) ? pnx_spec.loop_times : 1;
+      auto push = [&](int li, bool add) {
+        pair_runs.push_back(pnx_layers[li]);
+        pair_runs.back().add_x0 = add;
+      };
+      for (int li = 0; li < (passes > 1 ? a : L); ++li) push(li, false);
+      if (passes > 1) {
+        for (int p = 0; p < passes; ++p)
+          for (int li = a; li < b; ++li) push(li, p > 0 && li == a);
+        for (int li = b; li < L; ++li) push(li, false);
+        pnx_x0 = pnx_alloc<float>(T * W);
+      }
+      for (PnxLayer& r : pair_runs) {
+        const tgis_layer_spec& s = r.sp;
+        if (s.mixer == TGIS_MIXER_POOLED_ATTENTION)
+          cache_row_bytes += (size_t)s.kv_heads * (s.dim + s.vdim) * dt_size(pnx_dt);   // (+ the pooled rows: counted per block below)
+        else if (s.mixer == TGIS_MIXER_LATENT_ATTENTION)
+          cache_row_bytes += (size_t)r.g.row() * dt_size(pnx_dt);
+        else
+          r.st_S = pnx_alloc<float>((size_t)S_max * s.heads * s.dim * s.vdim, true);
+      }
+      if (pnx_spec.side_dim > 0) {
+        pnx_side = pnx_alloc_dt(V * pnx_layers.size() * pnx_spec.side_dim);
+        pnx_expected_tensors += 1;
+      }
+      pnx_hB = pnx_alloc_dt(T * W, true);
+    }
     // activations
     pnx_resid = pnx_alloc<float>(T * W);
     pnx_hA = pnx_alloc_dt(T * W, true);
@@ -1467,11 +1596,15 @@ struct tgis_engine {
       CK(cudaMemGetInfo(&free_b, &total_b));
       kv_bytes = (size_t)(free_b * (double)(c.gpu_mem_fraction > 0 ? c.gpu_mem_fraction : 0.85f));
     }
-    const size_t bytes_per_block = (size_t)KV_BLOCK * cache_row_bytes;
+    size_t bytes_per_block = (size_t)KV_BLOCK * cache_row_bytes;
+    for (PnxLayer& r : pair_runs)   // pooled rows of the windowed attention runs
+      if (r.sp.mixer == TGIS_MIXER_POOLED_ATTENTION)
+        bytes_per_block += (size_t)r.pa.rows_per_page() * r.pa.kv_heads * (r.pa.dim + r.pa.vdim) * dt_size(pnx_dt);
     size_t nb = std::min(kv_bytes / std::max<size_t>(bytes_per_block, 1), (size_t)S_max * bt_stride + 1);
     if (nb < 1) throw CudaError("cache too small for one block");
     num_blocks = (int)nb;
     for (PnxLayer& l : pnx_layers) {  // finite everywhere
+      if (pair_style) break;   // (the layer runs own the caches)
       if (l.sp.mixer == TGIS_MIXER_LATENT_ATTENTION) l.cache = pnx_alloc_dt(nb * KV_BLOCK * l.g.row(), true);
       if (l.sp.mixer == TGIS_MIXER_PARALLEL) {
         l.k_cache = pnx_alloc_dt(nb * KV_BLOCK * l.ca.kv_heads * l.ca.dim, true);
@@ -1484,6 +1617,17 @@ struct tgis_engine {
         } else {
           l.k_cache = pnx_alloc_dt(nb * KV_BLOCK * l.sa.kv_heads * l.sa.dim, true);
           l.v_cache = pnx_alloc_dt(nb * KV_BLOCK * l.sa.kv_heads * l.sa.vdim, true);
+        }
+      }
+    }
+    for (PnxLayer& r : pair_runs) {
+      if (r.sp.mixer == TGIS_MIXER_LATENT_ATTENTION) r.cache = pnx_alloc_dt(nb * KV_BLOCK * r.g.row(), true);
+      if (r.sp.mixer == TGIS_MIXER_POOLED_ATTENTION) {
+        r.k_cache = pnx_alloc_dt(nb * KV_BLOCK * r.pa.kv_heads * r.pa.dim, true);
+        r.v_cache = pnx_alloc_dt(nb * KV_BLOCK * r.pa.kv_heads * r.pa.vdim, true);
+        if (r.pa.pool > 0) {
+          r.pk_cache = pnx_alloc_dt(nb * r.pa.rows_per_page() * r.pa.kv_heads * r.pa.dim, true);
+          r.pv_cache = pnx_alloc_dt(nb * r.pa.rows_per_page() * r.pa.kv_heads * r.pa.vdim, true);
         }
       }
     }
@@ -1511,9 +1655,46 @@ struct tgis_engine {
     auto at = [&](void* base, size_t elem_off) { return reinterpret_cast<uint8_t*>(base) + elem_off * dt_size(pnx_dt); };
     auto mat = [&](void* dst, int64_t r, int64_t cc) { return place(dst, pnx_dt, r, cc, cc, 1); };
     auto vec = [&](float* dst, int64_t len) { return place(dst, DT_F32, len, 1, 1, 1); };
+    // a norm that carries ONE number: kept as a row of `len` equal entries
+    auto one = [&](float* dst, int64_t len) -> int {
+      if (n != 1) return bad_shape();
+      uint16_t bits = 0;
+      if (cudaMemcpy(&bits, tmp_src, sizeof(bits), cudaMemcpyDeviceToHost) != cudaSuccess) return fail("weight placement failed for " + name);
+      const uint32_t wide = (uint32_t)bits << 16;   // bf16 -> fp32
+      float v;
+      memcpy(&v, &wide, sizeof(v));
+      const std::vector<float> row((size_t)len, v);
+      if (cudaMemcpy(dst, row.data(), row.size() * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess)
+        return fail("weight placement failed for " + name);
+      pnx_loaded.insert(name);
+      return 0;
+    };
+    // [heads * dim, kv_rank] -> per head the transpose [kv_rank, dim]: the matrix that folds a key up-projection into the query
+    auto place_ukT = [&](void* dst, int heads, int dim, int kv_rank) -> int {
+      if (n != (int64_t)heads * dim * kv_rank) return bad_shape();
+      for (int h = 0; h < heads; ++h) {
+        const cudaError_t e = weight_place_launch(tmp_src + (size_t)h * dim * kv_rank, dim, kv_rank,
+                                                  at(dst, (size_t)h * kv_rank * dim), pnx_dt, 1, dim, 0);
+        if (e != cudaSuccess) return fail("weight placement failed for " + name);
+      }
+      if (cudaDeviceSynchronize() != cudaSuccess) return fail("weight placement failed for " + name);
+      pnx_loaded.insert(name);
+      return 0;
+    };
+    // one weight of `len` entries for all heads: kept once per head
+    auto per_head = [&](float* dst, int heads, int len) -> int {
+      if (n != len) return bad_shape();
+      for (int h = 0; h < heads; ++h)
+        if (weight_place_launch(tmp_src, len, 1, dst + (size_t)h * len, DT_F32, 1, 1, 0) != cudaSuccess)
+          return fail("weight placement failed for " + name);
+      if (cudaDeviceSynchronize() != cudaSuccess) return fail("weight placement failed for " + name);
+      pnx_loaded.insert(name);
+      return 0;
+    };
     if (name == "embed") return mat(pnx_embed, V, W);
     if (name == "head" && !tied_head) return mat(pnx_head, V, W);
-    if (name == "final.norm") return vec(pnx_final_norm, W);
+    if (name == "final.norm") return pair_style ? one(pnx_final_norm, W) : vec(pnx_final_norm, W);
+    if (name == "side.embed" && pnx_side != nullptr) return mat(pnx_side, V, (int64_t)pnx_layers.size() * pnx_spec.side_dim);
     if (name.size() < 3 || name[0] != 'l') return fail("unknown weight " + name);
     const size_t dot = name.find('.');
     if (dot == std::string::npos) return fail("unknown weight " + name);
@@ -1522,6 +1703,57 @@ struct tgis_engine {
     PnxLayer& l = pnx_layers[li];
     const tgis_layer_spec& s = l.sp;
     const std::string sub = name.substr(dot + 1);
+    if (pair_style) {
+      auto in_rows = [&](int col, int64_t r) { return mat(at(l.w_in, (size_t)col * W), r, W); };
+      const int64_t sd = pnx_spec.side_dim;
+      if (sub == "norm1") return one(l.norm1, W);
+      if (s.mlp == TGIS_MLP_DENSE_SILU) {
+        // gate / up rows interleave (row 2j = gate_j, row 2j + 1 = up_j): one product, the gated activation in its epilogue
+        if (sub == "norm2") return one(l.norm2, W);
+        if (sub == "mlp.gate") return place(l.w_gu, pnx_dt, s.ff, W, 2 * W, 1);
+        if (sub == "mlp.up") return place(at(l.w_gu, (size_t)W), pnx_dt, s.ff, W, 2 * W, 1);
+        if (sub == "mlp.down") return mat(l.w_d, W, s.ff);
+      }
+      if (sd > 0) {
+        if (sub == "side.gate") return mat(l.w_sg, sd, W);
+        if (sub == "side.proj") return mat(l.w_sp, W, sd);
+        if (sub == "side.norm") return vec(l.side_norm, W);
+      }
+      if (s.mixer == TGIS_MIXER_POOLED_ATTENTION) {
+        const int64_t H = s.heads, G = s.kv_heads;
+        if (sub == "mix.q") return in_rows(l.c_q, H * s.dim);
+        if (sub == "mix.k") return in_rows(l.c_k, G * s.dim);
+        if (sub == "mix.v") return in_rows(l.c_v, G * s.vdim);
+        if (l.in_bias != nullptr) {
+          if (sub == "mix.q.b") return vec(l.in_bias + l.c_q, H * s.dim);
+          if (sub == "mix.k.b") return vec(l.in_bias + l.c_k, G * s.dim);
+          if (sub == "mix.v.b") return vec(l.in_bias + l.c_v, G * s.vdim);
+        }
+        if (sub == "mix.o") return mat(l.w_o, W, H * s.vdim);
+      } else if (s.mixer == TGIS_MIXER_HGRN) {
+        const int64_t hd = (int64_t)s.heads * s.dim, hv = (int64_t)s.heads * s.vdim;
+        if (sub == "mix.q") return in_rows(l.c_q, hd);
+        if (sub == "mix.f") return in_rows(l.c_f, hd);
+        if (sub == "mix.v") return in_rows(l.c_v, hv);
+        if (sub == "mix.f.b") return vec(l.w0, hd);
+        if (sub == "mix.lower") return vec(l.u, hd);
+        if (sub == "mix.norm") return per_head(l.mm_norm, s.heads, s.vdim);
+        if (sub == "mix.o") return mat(l.w_o, W, hv);
+      } else {
+        const int64_t hd = s.dim + s.rot_dim;
+        if (sub == "mix.dq") return mat(l.w_down, s.q_rank, W);
+        if (sub == "mix.dkv") return mat(at(l.w_down, (size_t)s.q_rank * W), s.kv_rank + s.rot_dim, W);
+        if (sub == "mix.g" && l.out_gate) return mat(at(l.w_down, (size_t)(s.q_rank + s.kv_rank + s.rot_dim) * W), s.heads, W);
+        if (sub == "mix.dq.norm") return vec(l.qnorm, s.q_rank);
+        if (sub == "mix.dkv.norm") return vec(l.kvnorm, s.kv_rank);
+        if (sub == "mix.uq") return mat(l.w_uq, s.heads * hd, s.q_rank);
+        if (sub == "mix.uk") return place_ukT(l.w_ukT, s.heads, s.dim, s.kv_rank);
+        if (sub == "mix.uv") return mat(l.w_uv, (int64_t)s.heads * s.vdim, s.kv_rank);
+        if (sub == "mix.sink" && l.sink != nullptr) return vec(l.sink, s.heads);
+        if (sub == "mix.o") return mat(l.w_o, W, (int64_t)s.heads * s.vdim);
+      }
+      return fail("unknown layer weight " + name);
+    }
     if (sub == "norm1") return vec(l.norm1, W);
     if (s.mlp == TGIS_MLP_DENSE_GELU) {
       // gate / up rows interleave (row 2j = gate_j, row 2j + 1 = up_j): one product, the gated activation in its epilogue
@@ -1966,6 +2198,118 @@ struct tgis_engine {
     pnx_dump_resid(T);
   }
 
+  // One layer run of the parallel pair style (TGIS_STYLE_PARALLEL_PAIR).  On entry pnx_hA holds rms(x) * g1 and pnx_hB rms(x) * g2
+  // (operand type; hB only when the layer has a feed-forward):
+  //   x += mixer(hA) + ff(hB);   x += rms(P (gelu_tanh(G x) * e)) * w   (the per-layer token input; e: the layer's slice of the
+  //   token's row of the side table);   x += x0 if the NEXT run opens a pass of a loop
+  // and the tail leaves the next run's two normed inputs (after the last run: the final norm) behind.
+  void pair_layer(int ri, int T, int S) {
+    PnxLayer& l = pair_runs[ri];
+    const tgis_layer_spec& s = l.sp;
+    const int W = cfg.hidden, A = pnx_dt;
+    const float eps = pnx_spec.norm_eps;
+    const int32_t* d_tok = ds<int32_t>(off_tok);
+    const int32_t* d_pos = ds<int32_t>(off_pos);
+    const int32_t* d_slot = ds<int32_t>(off_slotmap);
+    const int32_t* d_tokslot = ds<int32_t>(off_tokslot);
+    const AttnSeq* d_seqs = ds<AttnSeq>(off_seqs);
+    const int32_t* d_bt = ds<int32_t>(off_bt);
+    const bool last = ri + 1 == (int)pair_runs.size();
+    const PnxLayer* nx = last ? nullptr : &pair_runs[ri + 1];
+    // ---- mixer -> pnx_o [T, width] fp32
+    if (s.mixer == TGIS_MIXER_POOLED_ATTENTION) {
+      const int H = s.heads, ld = l.in_cols;
+      pnx_gemm(pnx_hA, A, W, l.w_in, pnx_y1, DT_F32, ld, T, ld, W);
+      CK(poolattn_prep_launch(pnx_y1, ld, l.c_q, l.c_k, l.c_v, l.in_bias, l.pa, l.cos_sin, eps, d_pos, d_slot, pnx_q, l.k_cache,
+                              l.v_cache, A, T, stream));
+      CK(poolattn_pool_launch(l.k_cache, l.v_cache, l.pk_cache, l.pv_cache, A, d_seqs, S, d_bt, bt_stride, l.pa, step_max_q, stream));
+      CK(poolattn_launch(pnx_q, l.k_cache, l.v_cache, l.pk_cache, l.pv_cache, A, d_seqs, ds<LatentTile>(off_ltiles16), step_n_ltiles16,
+                         d_bt, bt_stride, pnx_oA, A, l.pa, stream));
+      n_launches += l.pa.pool > 0 ? 3 : 2;
+      pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
+    } else if (s.mixer == TGIS_MIXER_HGRN) {
+      const int H = s.heads, hd = H * s.dim, hv = H * s.vdim, ld = l.in_cols;
+      pnx_gemm(pnx_hA, A, W, l.w_in, pnx_y1, DT_F32, ld, T, ld, W);
+      OuterScan os{};
+      os.mode = OUTER_SCAN_HGRN;
+      os.q = pnx_y1 + l.c_q; os.k = nullptr; os.v = pnx_y1 + l.c_v; os.ldq = os.ldk = os.ldv = ld;
+      os.q_scale = 1.f;
+      os.decay_raw = pnx_y1 + l.c_f; os.ldd = ld; os.w0 = l.w0; os.u = l.u;
+      os.S = l.st_S;
+      os.out = flx_f1; os.ldo = hv;
+      os.heads = H; os.dim = s.dim; os.vdim = s.vdim;
+      (void)hd;
+      CK(outer_scan_launch(os, d_seqs, S, d_tokslot, stream));
+      CK(head_norm_gate_launch(flx_f1, hv, H, s.vdim, l.mm_norm, nullptr, 0, /*no gate*/ 2, eps, flx_op2, A, T, stream));
+      n_launches += 2;
+      pnx_gemm(flx_op2, A, hv, l.w_o, pnx_o, DT_F32, W, T, W, hv);
+    } else {  // TGIS_MIXER_LATENT_ATTENTION
+      const LatentGeom& g = l.g;
+      const int H = s.heads, hd = s.dim + s.rot_dim, D = g.row();
+      pnx_gemm(pnx_hA, A, W, l.w_down, pnx_y1, DT_F32, l.n_down(), T, l.n_down(), W);
+      CK(latent_prep_launch(pnx_y1, l.n_down(), g, l.qnorm, l.kvnorm, eps, d_pos, d_slot, l.cos_sin, pnx_cq, l.cache, A,
+                            l.out_gate ? pnx_gate : nullptr, T, stream));
+      pnx_gemm(pnx_cq, A, s.q_rank, l.w_uq, pnx_q, A, H * hd, T, H * hd, s.q_rank);
+      CK(latent_q_rope_launch(pnx_q, A, g, d_pos, l.cos_sin, pnx_qabs, T, stream));
+      {  // q_abs_h = W_uk,h^T q_plain_h  (one problem per head)
+        GemmAny a{};
+        a.X = pnx_q; a.W = l.w_ukT; a.Y = pnx_qabs;
+        a.x_dtype = A; a.w_dtype = A; a.y_dtype = DT_F32;
+        a.T = T; a.N = s.kv_rank; a.K = s.dim; a.ldx = H * hd; a.ldw = s.dim; a.ldy = H * D;
+        a.batch = H; a.x_bs = hd; a.w_bs = (long long)s.kv_rank * s.dim; a.y_bs = D;
+        CK(gemm_any_launch(a, stream));
+      }
+      int attn_launches = 0;
+      CK(latent_attn_launch(pnx_qabs, l.cache, A, d_seqs, ds<LatentTile>(off_ltiles), step_n_ltiles, d_bt, bt_stride, pnx_olat, A, g,
+                            stream, pnx_attn_ws, pnx_attn_ws_floats, step_max_kv, num_sms, &attn_launches));
+      n_launches += attn_launches - 1;
+      {  // o_h = W_uv,h o_lat_h  (times the head's gate where the layer has one)
+        GemmAny a{};
+        a.X = pnx_olat; a.W = l.w_uv; a.Y = pnx_oA;
+        a.x_dtype = A; a.w_dtype = A; a.y_dtype = A;
+        a.T = T; a.N = s.vdim; a.K = s.kv_rank; a.ldx = H * s.kv_rank; a.ldw = s.kv_rank; a.ldy = H * s.vdim;
+        a.batch = H; a.x_bs = s.kv_rank; a.w_bs = (long long)s.vdim * s.kv_rank; a.y_bs = s.vdim;
+        if (l.out_gate) { a.mode = GEMM_ANY_ROWSCALE; a.row_scale = pnx_gate; a.scale_ld = H; }
+        CK(gemm_any_launch(a, stream));
+      }
+      n_launches += 5;
+      pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
+    }
+    // ---- feed-forward on the second norm's rows -> pnx_yS
+    const bool has_ff = s.mlp == TGIS_MLP_DENSE_SILU;
+    if (has_ff) {
+      pnx_gemm(pnx_hB, A, W, l.w_gu, pnx_actS, A, s.ff, T, 2 * s.ff, W, GEMM_ANY_SWIGLU);
+      pnx_gemm(pnx_actS, A, s.ff, l.w_d, pnx_yS, DT_F32, W, T, W, s.ff);
+    }
+    const float* w_a = last ? pnx_final_norm : nx->norm1;
+    const float* w_b = (!last && nx->sp.mlp == TGIS_MLP_DENSE_SILU) ? nx->norm2 : nullptr;
+    const float* extra = (!last && nx->add_x0) ? pnx_x0 : nullptr;
+    const int sd = pnx_spec.side_dim;
+    GatedTail gt{};
+    gt.y_mix = pnx_o; gt.y_side = has_ff ? pnx_yS : nullptr;
+    gt.resid = pnx_resid; gt.eps = eps; gt.out_scale = 1.f; gt.out_dtype = A;
+    if (sd > 0) {
+      gt.resid_out = flx_mix;   // the token input's gate reads the stream itself
+    } else {
+      gt.extra = extra;
+      gt.w_next = w_a; gt.out = pnx_hA; gt.w_next2 = w_b; gt.out2 = pnx_hB;
+    }
+    CK(gated_tail_launch(gt, T, W, stream));
+    ++n_launches;
+    if (sd > 0) {
+      pnx_gemm(flx_mix, A, W, l.w_sg, pnx_rl, DT_F32, sd, T, sd, W);
+      CK(gelu_gate_rows_launch(pnx_rl, sd, d_tok, pnx_side, A, (int)pnx_layers.size() * sd, l.weights_of * sd, sd, pnx_cq, A, T, stream));
+      pnx_gemm(pnx_cq, A, sd, l.w_sp, pnx_yE, DT_F32, W, T, W, sd);
+      ResidTail rt{};
+      rt.y_main = pnx_yE; rt.w_post = l.side_norm; rt.w_off = 0.f; rt.mult = 1.f; rt.eps = eps;
+      rt.resid = pnx_resid; rt.extra = extra;
+      rt.w_pre = w_a; rt.out = pnx_hA; rt.out_dtype = A; rt.w_pre2 = w_b; rt.out2 = pnx_hB;
+      CK(resid_tail_launch(rt, T, W, stream));
+      n_launches += 2;
+    }
+    pnx_dump_resid(T);
+  }
+
   // embeddings + layer stack + final norm -> pnx_hA [T, hidden] (operand type), fp32 residual stream in pnx_resid
   void pnx_forward(int T, int S) {
     const int W = cfg.hidden, A = pnx_dt;
@@ -1977,6 +2321,15 @@ struct tgis_engine {
     const int32_t* d_bt = ds<int32_t>(off_bt);
     const LatentTile* d_tiles = ds<LatentTile>(off_ltiles);
     CK(embed_scale_f32_launch(d_tok, pnx_embed, A, pnx_spec.embed_scale, pnx_resid, T, W, cfg.vocab, stream));
+    if (pair_style) {
+      const PnxLayer& f = pair_runs[0];
+      if (pnx_x0 != nullptr) CK(cudaMemcpyAsync(pnx_x0, pnx_resid, (size_t)T * W * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+      CK(rmsnorm_f32_launch(pnx_resid, W, f.norm1, 0.f, pnx_hA, A, W, T, W, eps, stream));
+      if (f.sp.mlp == TGIS_MLP_DENSE_SILU) CK(rmsnorm_f32_launch(pnx_resid, W, f.norm2, 0.f, pnx_hB, A, W, T, W, eps, stream));
+      n_launches += 3;
+      for (int ri = 0; ri < (int)pair_runs.size(); ++ri) pair_layer(ri, T, S);
+      return;
+    }
     if (gated_style) {
       CK(rmsnorm_f32_launch(pnx_resid, W, pnx_layers[0].norm1, 0.f, rvp_n[0], DT_F32, W, T, W, eps, stream));
       CK(convert_f32_launch(rvp_n[0], pnx_hA, A, (size_t)T * W, stream));
@@ -2511,6 +2864,8 @@ struct tgis_engine {
     int32_t* bt = hs<int32_t>(off_bt);
     const int S = (int)batch.size();
     step_n_ltiles = 0;
+    step_n_ltiles16 = 0;
+    step_max_q = 0;
     step_max_kv = 0;
     for (int s = 0; s < S; ++s) {
       Request& r = *batch[s].r;
@@ -2539,6 +2894,12 @@ struct tgis_engine {
         LatentTile* lt = hs<LatentTile>(off_ltiles);
         for (int q0 = 0; q0 < q_len; q0 += pnx_tile_tokens)
           lt[step_n_ltiles++] = LatentTile{s, q0, std::min(pnx_tile_tokens, q_len - q0), 0};
+        if (pair_style) {
+          LatentTile* lt16 = hs<LatentTile>(off_ltiles16);
+          for (int q0 = 0; q0 < q_len; q0 += POOLATTN_TILE)
+            lt16[step_n_ltiles16++] = LatentTile{s, q0, std::min(POOLATTN_TILE, q_len - q0), 0};
+          step_max_q = std::max(step_max_q, q_len);
+        }
       }
       if (q_len == 1) {
         decids[n_dec++] = s;
@@ -3087,7 +3448,7 @@ int tgis_abi_version(void) { return TGIS_ABI_VERSION; }
 int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
   if (!cfg || !out) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch == TGIS_ARCH_PONENEX || cfg->arch == TGIS_ARCH_FALERAX || cfg->arch == TGIS_ARCH_REVEPEL)
+  if (cfg->arch == TGIS_ARCH_PONENEX || cfg->arch == TGIS_ARCH_FALERAX || cfg->arch == TGIS_ARCH_REVEPEL || cfg->arch == TGIS_ARCH_SIKAZEN)
     return fail("this architecture is described layer by layer: use tgis_engine_create_spec");
   if (cfg->arch != TGIS_ARCH_LLAMA && cfg->arch != TGIS_ARCH_OPT) return fail("unknown arch");
   if (cfg->arch == TGIS_ARCH_OPT) {
@@ -3134,7 +3495,7 @@ int tgis_engine_create(const tgis_config* cfg, tgis_engine** out) {
 int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec, tgis_engine** out) {
   if (!cfg || !spec || !out || !spec->layers) return fail("null argument");
   if (cfg->abi_version != TGIS_ABI_VERSION) return fail("ABI version mismatch");
-  if (cfg->arch != TGIS_ARCH_PONENEX && cfg->arch != TGIS_ARCH_FALERAX && cfg->arch != TGIS_ARCH_REVEPEL)
+  if (cfg->arch != TGIS_ARCH_PONENEX && cfg->arch != TGIS_ARCH_FALERAX && cfg->arch != TGIS_ARCH_REVEPEL && cfg->arch != TGIS_ARCH_SIKAZEN)
     return fail("tgis_engine_create_spec: arch must be a layer-list architecture");
   if (spec->n_layers < 1 || spec->n_layers > 4096) return fail("bad n_layers");
   if (spec->dtype != TGIS_DTYPE_BF16 && spec->dtype != TGIS_DTYPE_F32) return fail("dtype must be bf16 or fp32");
@@ -3146,6 +3507,32 @@ int tgis_engine_create_spec(const tgis_config* cfg, const tgis_model_spec* spec,
     const tgis_layer_spec& s = spec->layers[i];
     const std::string at = " (layer " + std::to_string(i) + ")";
     const bool post = (spec->style & TGIS_STYLE_POST_NORM) != 0;
+    if ((spec->style & TGIS_STYLE_PARALLEL_PAIR) != 0) {
+      if (spec->style != TGIS_STYLE_PARALLEL_PAIR) return fail("the parallel pair style has its own norm placement and an untied head");
+      if (spec->side_dim < 0 || spec->side_dim > 4096) return fail("bad width of the per-layer token input");
+      if (spec->loop_times > 1 && (spec->loop_start < 0 || spec->loop_stop > spec->n_layers || spec->loop_start >= spec->loop_stop))
+        return fail("the looped span must lie inside the layer list");
+      if (spec->loop_times > 64) return fail("more than 64 passes of a loop");
+      if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_DENSE_SILU) return fail("unknown feed-forward kind" + at);
+      if (s.mlp == TGIS_MLP_DENSE_SILU && s.ff < 1) return fail("bad feed-forward width" + at);
+      if (s.rot_dims > 0 && !(s.rot_base > 0.f)) return fail("bad rotary base" + at);
+      if (s.mixer == TGIS_MIXER_POOLED_ATTENTION) {
+        if (s.heads < 1 || s.kv_heads < 1 || s.heads % s.kv_heads != 0 || s.dim < 1 || s.vdim < 1 || s.vdim > POOLATTN_MAX_VDIM ||
+            s.dim > 512)
+          return fail("bad attention sizes" + at);
+        if (s.rot_dims < 0 || s.rot_dims > s.dim || (s.rot_dims & 1)) return fail("rot.dims must be even and <= dim" + at);
+        if (s.pool > 0 && s.window <= 0) return fail("pooled blocks need a window" + at);
+      } else if (s.mixer == TGIS_MIXER_HGRN) {
+        if (s.heads < 1 || s.dim < 1 || s.dim > OUTER_SCAN_MAX_DIM || s.vdim < 1) return fail("bad hgrn sizes" + at);
+      } else if (s.mixer == TGIS_MIXER_LATENT_ATTENTION) {
+        if (s.heads < 1 || s.dim < 1 || s.rot_dim < 0 || s.vdim < 1 || s.kv_rank < 1 || s.q_rank < 1) return fail("bad mixer sizes" + at);
+        if (s.kv_rank > 512) return fail("kv_rank > 512 unsupported" + at);
+        if (s.rot_dims < 0 || s.rot_dims > s.rot_dim || (s.rot_dims & 1)) return fail("rot.dims must be even and <= rot_dim" + at);
+      } else {
+        return fail("unknown mixer type" + at);
+      }
+      continue;
+    }
     if ((spec->style & TGIS_STYLE_PARALLEL_GATED) != 0) {
       if (post || (spec->style & TGIS_STYLE_TIED_HEAD) != 0) return fail("the parallel gated style has its own norm placement and an untied head");
       if (s.mlp != TGIS_MLP_NONE && s.mlp != TGIS_MLP_MOE_SIGMOID) return fail("unknown feed-forward kind" + at);

@@ -275,6 +275,7 @@ cudaError_t embed_scale_f32_launch(const int32_t* token_ids, const void* table, 
 //             = (rmsnorm(y_main[t]) * w_main + rmsnorm(y_pair[t]) * w_pair) / 2             (y_pair != nullptr: two mixers
 //                                                                                            side by side, plain weights)
 //   cast_out != 0 (and w_pre == nullptr): out[t] = resid[t] in the operand type -- the next sublayer reads the stream itself
+//   extra != nullptr: resid[t] += extra[t] after the update;  w_pre2 / out2: out2[t] = rmsnorm(resid[t]) * (w_off + w_pre2)
 struct ResidTail {
   const float* y_main;
   const float* y_rows; const int32_t* inv; const float* mix_w; int top;
@@ -284,6 +285,8 @@ struct ResidTail {
   float mult, w_off, eps;
   const float* y_pair; const float* w_main; const float* w_pair;
   int cast_out;
+  const float* extra;                 // optional fp32 [T, hidden]: added to resid after the sublayer's update, before the pre-norm
+  const float* w_pre2; void* out2;    // optional second pre-norm of the same rows with another weight (two sublayers side by side)
 };
 cudaError_t resid_tail_launch(const ResidTail& a, int T, int hidden, cudaStream_t stream);
 // Tail of a layer whose mixer and feed-forward run side by side on ONE normed input and are gated per channel, row per CTA:
@@ -300,8 +303,15 @@ struct GatedTail {
   const float* w_next; float eps, out_scale;
   float* n_f32; void* out; int out_dtype;
   const float* n_cur; float* prev_state; const int32_t* tok_slot;
+  const float* w_next2; void* out2;   // optional: the same normed rows under a second weight (operand type)
+  void* resid_out;                    // optional: the updated stream itself in the operand type
+  const float* extra;                 // optional fp32 [T, hidden]: added to the stream together with the update
 };
 cudaError_t gated_tail_launch(const GatedTail& a, int T, int hidden, cudaStream_t stream);
+// out[t, j] = gelu_tanh(z[t, j]) * table[tok[t], col0 + j]   j < n: a gate on per-token side rows (z fp32 [T, ldz], table DT_*
+// [vocab, ld_table], out DT_* [T, n])
+cudaError_t gelu_gate_rows_launch(const float* z, int ldz, const int32_t* token_ids, const void* table, int table_dtype,
+                                  int ld_table, int col0, int n, void* out, int out_dtype, int T, cudaStream_t stream);
 // rows of any DT_* matrix: out[r, :] = x[rows[r], :]
 cudaError_t gather_rows_any_launch(const void* x, const int32_t* rows, void* out, int R, int hidden, int dtype,
                                    cudaStream_t stream);
@@ -319,6 +329,9 @@ struct LatentGeom {
   int heads, dim, rot_dim, vdim, kv_rank, q_rank, window;
   int rot_dims;      // the first rot_dims of the rot_dim rotated dims turn ("rotate half": i pairs with i + rot_dims / 2)
   float scale;
+  int interleaved;   // != 0: the rotated entries pair as (2i, 2i + 1) instead of (i, i + rot_dims / 2)
+  const float* sink; // fp32 [heads] or nullptr: the softmax denominator of head h also holds exp(sink[h]) (no key, no value,
+                     // not scaled, counted once)
   __host__ __device__ int row() const { return kv_rank + rot_dim; }   // cache row / absorbed query length
 };
 // y [T, ldy] fp32 = the fused down-projection [q latent (q_rank) | kv latent (kv_rank) | k_rot (rot_dim) | gate (heads)]:
@@ -392,6 +405,40 @@ cudaError_t sigattn_launch(const void* q, const void* k_cache, const void* v_cac
                            const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
                            const float* head_bias, void* out, int out_dtype, const SigAttnGeom& g, cudaStream_t stream);
 
+// ---- attention_pooled.cu: grouped-query softmax attention over a sliding window plus pooled blocks of what left it -----
+// Per head: rotary turn of the first rot_dims entries of every query and key ("rotate half": i pairs with i + rot_dims / 2),
+// then (unit_norm != 0) q and k divided by their root mean square over dim; score = scale * q . k.  Query i sees the tokens j
+// with 0 <= i - j < window one by one and, with pool > 0, every block b of `pool` consecutive positions that ends at or
+// before i - window (b * pool + pool - 1 <= i - window) through ONE key and ONE value: the means of the block's cached
+// keys and of its values.  Tokens behind the window whose block is not complete by then are not seen.  Tokens and blocks
+// share one softmax.  window <= 0: every earlier position, no blocks.  Query head h reads key/value head h / (heads / kv_heads).
+struct PoolAttnGeom {
+  int heads, kv_heads, dim, vdim, window, pool;
+  int rot_dims;
+  float scale;
+  int unit_norm;
+  __host__ __device__ int rows_per_page() const { return pool > 0 ? (KV_BLOCK + pool - 1) / pool : 0; }   // pooled rows a cache page owns
+};
+constexpr int POOLATTN_TILE = 16;      // query tokens per CTA
+constexpr int POOLATTN_MAX_VDIM = 512; // value columns per head the FMA kernel's accumulators cover
+// y fp32 [T, ldy] holds q at column q_off (heads * dim), k at k_off (kv_heads * dim), v at v_off (kv_heads * vdim); bias fp32
+// (q | k | v, in that order, or nullptr) is added first.  cos_sin fp32 [max_pos][rot_dims] = cos | sin.  q_out DT_* [T, heads * dim];
+// cache rows K [num_blocks][KV_BLOCK][kv_heads * dim], V [..][kv_heads * vdim] at slot[t].
+cudaError_t poolattn_prep_launch(const float* y, int ldy, int q_off, int k_off, int v_off, const float* bias,
+                                 const PoolAttnGeom& g, const float* cos_sin, float eps, const int32_t* positions,
+                                 const int32_t* slot_mapping, void* q_out, void* k_cache, void* v_cache, int dtype, int T,
+                                 cudaStream_t stream);
+// The blocks that this step's tokens complete: pooled row b = mean over the block's rows as the cache holds them (fp32 sum
+// in position order).  Block b of a sequence lives in the page of its FIRST token, page p = b * pool / KV_BLOCK, at index
+// b - ceil(p * KV_BLOCK / pool): pk [num_blocks][rows_per_page()][kv_heads * dim], pv [..][kv_heads * vdim], DT_*.
+cudaError_t poolattn_pool_launch(const void* k_cache, const void* v_cache, void* pk, void* pv, int dtype,
+                                 const AttnSeq* seqs, int n_seqs, const int32_t* block_table, int bt_stride,
+                                 const PoolAttnGeom& g, int max_q_len, cudaStream_t stream);
+// out DT_* [T, heads * vdim]
+cudaError_t poolattn_launch(const void* q, const void* k_cache, const void* v_cache, const void* pk, const void* pv, int dtype,
+                            const AttnSeq* seqs, const LatentTile* tiles, int n_tiles, const int32_t* block_table,
+                            int bt_stride, void* out, int out_dtype, const PoolAttnGeom& g, cudaStream_t stream);
+
 // ---- recurrent.cu: mixers that carry a state from token to token ----------------------------------------------------
 // Every sequence owns one state slot per layer (the engine's sequence slot).  A kernel reads the slot's state for the first
 // token of a portion unless that token's position is 0 (then the state is zero: a slot needs no clearing when it is handed
@@ -429,7 +476,10 @@ cudaError_t selective_scan_launch(const SelScan& a, const AttnSeq* seqs, int n_s
 //   OUTER_SCAN_SSD:    dt = softplus(step_raw + step_b), S <- exp(-exp(A_log_h) dt) S + dt k v^T;  o = S^T q + D_h v
 //                      (one decay per head and token; the query reads the state after the token's update; q / k heads may be
 //                      shared by groups of heads: qk_heads)
-constexpr int OUTER_SCAN_DECAY = 0, OUTER_SCAN_GATED = 1, OUTER_SCAN_SSD = 2;
+//   OUTER_SCAN_HGRN:   f = l + (1 - l) sigmoid(decay_raw + w0), l = u (a lower bound per head and key channel);
+//                      S <- diag(f) S + (1 - f) v^T;  o = S^T silu(q)   (no key: what the gate forgets is what it writes; the
+//                      query reads the state after the token's update)
+constexpr int OUTER_SCAN_DECAY = 0, OUTER_SCAN_GATED = 1, OUTER_SCAN_SSD = 2, OUTER_SCAN_HGRN = 3;
 constexpr int OUTER_SCAN_MAX_DIM = 256;
 struct OuterScan {
   int mode;
@@ -446,7 +496,7 @@ struct OuterScan {
 };
 cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seqs, const int32_t* tok_slot,
                               cudaStream_t stream);
-// out[t, h, :] = rmsnorm(o[t, h, :]) * w[h, :] * act(gate[t, h, :])    act: 0 sigmoid, 1 silu
+// out[t, h, :] = rmsnorm(o[t, h, :]) * w[h, :] * act(gate[t, h, :])    act: 0 sigmoid, 1 silu, 2 none (gate may be nullptr)
 // gate_first != 0: out[t, h, :] = rmsnorm(o[t, h, :] * act(gate[t, h, :])) * w[h, :]   (the gate enters the norm)
 cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, const float* w, const float* gate,
                                   int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream,

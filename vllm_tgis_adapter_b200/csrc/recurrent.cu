@@ -246,7 +246,7 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
   float u_r[RPT];   // DECAY: the bonus u of this thread's rows; GATED: the normaliser n of its rows (the same in every lane)
   float m_run = 0.f;
   const float ssd_rate = MODE == OUTER_SCAN_SSD ? -expf(a.A_log[h]) : 0.f, ssd_skip = MODE == OUTER_SCAN_SSD ? a.D[h] : 0.f;
-  if (MODE == OUTER_SCAN_SSD) {
+  if (MODE == OUTER_SCAN_SSD || MODE == OUTER_SCAN_HGRN) {
 #pragma unroll
     for (int j = 0; j < RPT; ++j) u_r[j] = 0.f;
   } else if (MODE == OUTER_SCAN_DECAY) {
@@ -276,14 +276,15 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
     const bool tok = st_tt < nt;
     const size_t row = (size_t)(sq.q_start + t0 + (tok ? st_tt : 0));
     const float* qr = a.q + row * a.ldq + (size_t)hq * D;
-    const float* kr = a.k + row * a.ldk + (size_t)hq * D;
+    const float* kr = MODE == OUTER_SCAN_HGRN ? nullptr : a.k + row * a.ldk + (size_t)hq * D;
 #pragma unroll
     for (int e = 0; e < EPT; ++e) {
       const int i = st_l + e * TPT;
       const bool in = tok && i < D;
       pq[e] = in ? qr[i] : 0.f;
-      pk[e] = in ? kr[i] : 0.f;
-      if (MODE == OUTER_SCAN_DECAY) pd[e] = in ? a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i] : 0.f;
+      pk[e] = in ? (MODE == OUTER_SCAN_HGRN ? a.u[(size_t)h * D + i] : kr[i]) : 0.f;   // HGRN: the gate's lower bound
+      if (MODE == OUTER_SCAN_DECAY || MODE == OUTER_SCAN_HGRN)
+        pd[e] = in ? a.decay_raw[row * a.ldd + (size_t)h * D + i] + a.w0[(size_t)h * D + i] : 0.f;
     }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
@@ -306,9 +307,15 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
       for (int e = 0; e < EPT; ++e) {
         const int i = st_l + e * TPT;
         if (i < D) {
-          v3[i] = pq[e] * a.q_scale;
-          v3[D + i] = pk[e];
-          if (MODE == OUTER_SCAN_DECAY) v3[2 * D + i] = expf(-expf(pd[e]));
+          if (MODE == OUTER_SCAN_HGRN) {   // q = silu(.), f = l + (1 - l) sigmoid(.), and what is written: 1 - f
+            v3[i] = silu_f(pq[e]) * a.q_scale;
+            v3[D + i] = (1.f - pk[e]) * sigmoid_f(-pd[e]);                 // 1 - f without the cancellation near f = 1
+            v3[2 * D + i] = pk[e] + (1.f - pk[e]) * sigmoid_f(pd[e]);
+          } else {
+            v3[i] = pq[e] * a.q_scale;
+            v3[D + i] = pk[e];
+            if (MODE == OUTER_SCAN_DECAY) v3[2 * D + i] = expf(-expf(pd[e]));
+          }
         }
       }
     }
@@ -337,6 +344,15 @@ outer_scan_kernel(OuterScan a, const AttnSeq* __restrict__ seqs, const int32_t* 
             const float kv = v3[D + i] * vc;
             o = fmaf(v3[i], fmaf(u_r[j], kv, S[j]), o);
             S[j] = fmaf(v3[2 * D + i], S[j], kv);
+          }
+        }
+      } else if (MODE == OUTER_SCAN_HGRN) {
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+          const int i = g + j * OS_GROUPS;
+          if (i < D) {
+            S[j] = fmaf(v3[2 * D + i], S[j], v3[D + i] * vc);
+            o = fmaf(v3[i], S[j], o);
           }
         }
       } else if (MODE == OUTER_SCAN_SSD) {
@@ -607,8 +623,11 @@ head_norm_gate_kernel(const float* __restrict__ o, int ldo, int heads, int vdim,
   for (int i = lane; i < vdim; i += 32) ss = fmaf(orow[i], orow[i], ss);
   const float rs = 1.f / sqrtf(warp_sum_f(ss) / (float)vdim + eps);
   for (int i = lane; i < vdim; i += 32) {
-    const float gl = gate[(size_t)t * ldg + (size_t)h * vdim + i];
-    const float gv = act == 1 ? silu_f(gl) : sigmoid_f(gl);
+    float gv = 1.f;
+    if (act != 2) {
+      const float gl = gate[(size_t)t * ldg + (size_t)h * vdim + i];
+      gv = act == 1 ? silu_f(gl) : sigmoid_f(gl);
+    }
     st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * rs * w[(size_t)h * vdim + i] * gv);
   }
 }
@@ -627,7 +646,7 @@ head_norm_gate_wide_kernel(const float* __restrict__ o, int ldo, int heads, int 
   float ss = 0.f;
   for (int i = tid; i < vdim; i += 256) {
     float v = orow[i];
-    if (gate_first) v *= act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
+    if (gate_first && act != 2) v *= act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
     ss = fmaf(v, v, ss);
   }
   ss = warp_sum_f(ss);
@@ -638,7 +657,7 @@ head_norm_gate_wide_kernel(const float* __restrict__ o, int ldo, int heads, int 
   for (int r = 0; r < 8; ++r) tot += red[r];   // the same order in every thread
   const float rs = 1.f / sqrtf(tot / (float)vdim + eps);
   for (int i = tid; i < vdim; i += 256) {
-    const float gv = act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
+    const float gv = act == 2 ? 1.f : act == 1 ? silu_f(grow[i]) : sigmoid_f(grow[i]);
     st_op(out, out_dtype, (size_t)t * out_ld + (size_t)h * vdim + i, orow[i] * gv * rs * w[(size_t)h * vdim + i]);
   }
 }
@@ -718,6 +737,10 @@ cudaError_t outer_scan_launch(const OuterScan& a, const AttnSeq* seqs, int n_seq
     if (a.step_raw == nullptr || a.step_b == nullptr || a.A_log == nullptr || a.D == nullptr) return cudaErrorInvalidValue;
     return outer_scan_mode<OUTER_SCAN_SSD>(a, seqs, n_seqs, tok_slot, stream);
   }
+  if (a.mode == OUTER_SCAN_HGRN) {
+    if (a.decay_raw == nullptr || a.w0 == nullptr || a.u == nullptr) return cudaErrorInvalidValue;
+    return outer_scan_mode<OUTER_SCAN_HGRN>(a, seqs, n_seqs, tok_slot, stream);
+  }
   return a.mode == OUTER_SCAN_GATED ? outer_scan_mode<OUTER_SCAN_GATED>(a, seqs, n_seqs, tok_slot, stream)
                                     : outer_scan_mode<OUTER_SCAN_DECAY>(a, seqs, n_seqs, tok_slot, stream);
 }
@@ -726,6 +749,8 @@ cudaError_t head_norm_gate_launch(const float* o, int ldo, int heads, int vdim, 
                                   int ldg, int act, float eps, void* out, int out_dtype, int T, cudaStream_t stream,
                                   int gate_first) {
   if (T <= 0) return cudaSuccess;
+  if (act == 2) gate_first = 0;
+  else if (gate == nullptr) return cudaErrorInvalidValue;
   if (vdim >= 1024 && heads <= 65535)
     return launch_k(head_norm_gate_wide_kernel, dim3(T, heads), dim3(256), 0, stream, o, ldo, heads, vdim, w, gate, ldg, act, eps, out,
                     out_dtype, heads * vdim, gate_first);

@@ -10,12 +10,14 @@ import ctypes as C
 import os
 from pathlib import Path
 
-ABI_VERSION = 10
-ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX, ARCH_FALERAX, ARCH_REVEPEL = 0, 1, 2, 3, 4
+ABI_VERSION = 11
+ARCH_LLAMA, ARCH_OPT, ARCH_PONENEX, ARCH_FALERAX, ARCH_REVEPEL, ARCH_SIKAZEN = 0, 1, 2, 3, 4, 5
 MIXER_LATENT_ATTENTION, MIXER_PARALLEL, MIXER_SELECTIVE_SCAN, MIXER_WKV = 1, 2, 3, 4
 MIXER_SIGMOID_ATTENTION, MIXER_SSD, MIXER_CHANNEL_DELTA = 5, 6, 7
-MLP_NONE, MLP_MOE, MLP_DENSE_GELU, MLP_MOE_SIGMOID = 0, 1, 2, 3
-STYLE_POST_NORM, STYLE_TIED_HEAD, STYLE_PARALLEL_GATED = 1, 2, 4
+MIXER_POOLED_ATTENTION, MIXER_HGRN = 8, 9
+MLP_NONE, MLP_MOE, MLP_DENSE_GELU, MLP_MOE_SIGMOID, MLP_DENSE_SILU = 0, 1, 2, 3, 4
+LAYER_ROT_INTERLEAVED, LAYER_SINK, LAYER_NO_OUT_GATE, LAYER_QKV_BIAS, LAYER_UNIT_QK = 1, 2, 4, 8, 16
+STYLE_POST_NORM, STYLE_TIED_HEAD, STYLE_PARALLEL_GATED, STYLE_PARALLEL_PAIR = 1, 2, 4, 8
 DTYPE_BF16, DTYPE_F32 = 0, 1
 MAX_REQUEST_ID = 96
 MAX_TOPN = 12
@@ -49,6 +51,7 @@ class TgisLayerSpec(C.Structure):
         ("decay_rank", C.c_int32), ("reserved", C.c_int32),
         ("kv_from", C.c_int32), ("yarn_factor", C.c_float), ("yarn_original", C.c_float), ("yarn_fast", C.c_float),
         ("yarn_slow", C.c_float), ("groups", C.c_int32), ("norm_groups", C.c_int32), ("gate_rank", C.c_int32),
+        ("pool", C.c_int32), ("rot_linear", C.c_float), ("flags", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -77,7 +80,8 @@ class TgisModelSpec(C.Structure):
     _fields_ = [
         ("n_layers", C.c_int32), ("dtype", C.c_int32), ("embed_scale", C.c_float), ("residual_mult", C.c_float),
         ("norm_eps", C.c_float), ("style", C.c_int32), ("layers", C.POINTER(TgisLayerSpec)),
-        ("logit_scale", C.c_float), ("reserved", C.c_int32),
+        ("logit_scale", C.c_float), ("side_dim", C.c_int32),
+        ("loop_start", C.c_int32), ("loop_stop", C.c_int32), ("loop_times", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

@@ -30,16 +30,18 @@ class ModelConfig:
     rms_eps: float = 1e-5
     max_model_len: int = 2048
     arch: str = "llama"
-    # arch "ponenex" (engine/ponenex.py), "falerax" (engine/falerax.py) and "revepel" (engine/revepel.py): the layers are described one by one;
+    # arch "ponenex" (engine/ponenex.py), "falerax" (engine/falerax.py), "revepel" (engine/revepel.py) and "sikazen" (engine/sikazen.py): the layers are described one by one;
     # n_q_heads / n_kv_heads / ffn are unused
     layers: list | None = None          # list[ponenex.LayerSpec] / list[falerax.LayerSpec] / list[revepel.LayerSpec]
     embed_scale: float = 1.0
     logit_scale: float = 1.0            # logits = head x * logit_scale
     residual_mult: float = 1.0
     dtype: str = "bfloat16"             # "bfloat16" | "float32" (layer-list architectures only)
+    side_dim: int = 0                   # arch "sikazen": columns of the side table one layer reads (0: no per-layer token input)
+    loop: tuple = (0, 0, 1)             # arch "sikazen": layers [start, stop) run `times` passes in a row
 
 
-LAYER_LIST_ARCHS = ("ponenex", "falerax", "revepel")   # created with tgis_engine_create_spec; bfloat16 or float32
+LAYER_LIST_ARCHS = ("ponenex", "falerax", "revepel", "sikazen")   # created with tgis_engine_create_spec; bfloat16 or float32
 
 
 # Named architectures (real dims; this offline build runs them on synthetic weights — SURVEY.md §0)
@@ -71,6 +73,10 @@ def cache_block_bytes(mc: ModelConfig) -> int:
     if mc.arch == "ponenex":
         esz = 4 if mc.dtype == "float32" else 2
         return KV_BLOCK_TOKENS * esz * sum(l.kv_rank + l.rot_dim for l in mc.layers)
+    if mc.arch == "sikazen":
+        from .sikazen import cache_block_elems
+
+        return max((4 if mc.dtype == "float32" else 2) * cache_block_elems(mc, KV_BLOCK_TOKENS), 1)
     if mc.arch in ("falerax", "revepel"):
         if mc.arch == "falerax":
             from .falerax import cache_row_elems
@@ -164,7 +170,7 @@ class NativeEngine:
         cfg.use_cuda_graphs, cfg.debug_gemm_ref, cfg.seed = int(use_cuda_graphs), 1 if debug_gemm_ref else 0, seed
         cfg.max_loras, cfg.max_lora_rank = int(max_loras), int(max_lora_rank) if max_loras else 0
         archs = {"llama": _lib.ARCH_LLAMA, "opt": _lib.ARCH_OPT, "ponenex": _lib.ARCH_PONENEX, "falerax": _lib.ARCH_FALERAX,
-                 "revepel": _lib.ARCH_REVEPEL}
+                 "revepel": _lib.ARCH_REVEPEL, "sikazen": _lib.ARCH_SIKAZEN}
         if model.arch not in archs:
             raise EngineError(f"unknown architecture {model.arch!r}")
         cfg.arch = archs[model.arch]
@@ -175,6 +181,8 @@ class NativeEngine:
                 from .ponenex import model_spec
             elif model.arch == "falerax":
                 from .falerax import model_spec
+            elif model.arch == "sikazen":
+                from .sikazen import model_spec
             else:
                 from .revepel import model_spec
 
@@ -193,6 +201,8 @@ class NativeEngine:
         t = tensor.detach()
         if t.dtype != torch.bfloat16:
             t = t.to(torch.bfloat16)
+        if t.dim() == 0:
+            t = t.reshape(1)   # a single number (norms that carry one weight for all channels)
         t = t.contiguous()
         rows = t.shape[0]
         cols = t.numel() // rows if rows else 0

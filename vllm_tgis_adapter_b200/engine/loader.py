@@ -32,6 +32,10 @@ def model_config_from_hf(path: Path, max_model_len: int | None, dtype: str = "bf
         from .revepel import checkpoint_shapes, model_config_from_json
 
         return model_config_from_json(cfg, max_model_len, dtype, checkpoint_shapes(path))
+    if cfg.get("architecture") == "Sikazen":
+        from .sikazen import model_config_from_json
+
+        return model_config_from_json(cfg, max_model_len, dtype)
     archs = cfg.get("architectures") or []
     if cfg.get("model_type") == "opt" or any("OPT" in a for a in archs):
         return _opt_model_config(cfg, max_model_len)
@@ -104,6 +108,8 @@ def load_synthetic_weights(eng: NativeEngine, mc: ModelConfig, seed: int, device
             from .ponenex import iter_synthetic_weights
         elif mc.arch == "falerax":
             from .falerax import iter_synthetic_weights
+        elif mc.arch == "sikazen":
+            from .sikazen import iter_synthetic_weights
         else:
             from .revepel import iter_synthetic_weights
 
@@ -191,8 +197,9 @@ def _resolve_model(args):
     from .falerax import PRESETS as FALERAX_PRESETS
     from .ponenex import PRESETS as PONENEX_PRESETS
     from .revepel import PRESETS as REVEPEL_PRESETS
+    from .sikazen import PRESETS as SIKAZEN_PRESETS
 
-    PONENEX_PRESETS = {**PONENEX_PRESETS, **FALERAX_PRESETS, **REVEPEL_PRESETS}   # the presets of the layer-list architectures
+    PONENEX_PRESETS = {**PONENEX_PRESETS, **FALERAX_PRESETS, **REVEPEL_PRESETS, **SIKAZEN_PRESETS}   # the presets of the layer-list architectures
     if args.model in PRESETS or args.model in PONENEX_PRESETS:
         if not args.synthetic_weights:
             raise ValueError(f"--model {args.model} is a preset name: pass --synthetic-weights or a model directory")
