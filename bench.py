@@ -770,11 +770,12 @@ def run_ours(args) -> dict | None:
 
 
 # ------------------------------------------------------------------------------------------------ --arch-compare
-# Prefill and decode throughput of the layer-list families (Ponenex, Falerax) beside the closest existing family (Llama) at equal hidden size, layer
+# Prefill and decode throughput of the layer-list families (Ponenex, Falerax, Revepel, Sikazen) beside the closest existing family (Llama) at equal hidden size, layer
 # count and active feed-forward width, random weights, device-timed (the engine's CUDA events around every step).  Not the
 # default workload: `python bench.py --arch-compare` prints its own JSON line; the default JSON line is untouched.
 ARCH_COMPARE = [("ponenex-1k", "llama-cmp-1k"), ("ponenex-2k", "llama-cmp-2k"), ("falerax-1k", "llama-cmp-1k"),
-                ("falerax-2k", "llama-cmp-2k"), ("revepel-1k", "llama-cmp-1k"), ("revepel-2k", "llama-cmp-2k")]
+                ("falerax-2k", "llama-cmp-2k"), ("revepel-1k", "llama-cmp-1k"), ("revepel-2k", "llama-cmp-2k"),
+                ("sikazen-1k", "llama-cmp-1k"), ("sikazen-2k", "llama-cmp-2k")]
 
 
 def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
@@ -837,6 +838,31 @@ def _arch_work(mc, B: int, ctx: float) -> tuple[float, float]:
             # (a layer that shares another's rows reads them again), and reads + writes its fp32 state
             bytes_ += 2.0 * (dense + gates + 2 * h * (experts_touched * l.expert_ff + l.shared_ff)) + B * (2.0 * keys * cache + 8.0 * state)
         return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
+    if mc.arch == "sikazen":
+        from vllm_tgis_adapter_b200.engine.sikazen import layer_runs
+
+        flops = bytes_ = 0.0
+        for i in layer_runs(mc):   # a looped layer runs (and streams its weights) once per pass
+            l = mc.layers[i]
+            if l.kind == "attention":
+                keys = min(ctx, l.window or ctx) + (max(ctx - l.window, 0) / l.pool if l.window and l.pool else 0)
+                dense = h * (l.heads * l.dim + l.kv_heads * (l.dim + l.vdim)) + l.heads * l.vdim * h
+                scan, state, cache = l.heads * keys * (l.dim + l.vdim), 0, keys * l.kv_heads * (l.dim + l.vdim)
+            elif l.kind == "latent_attention":
+                row = l.kv_rank + l.rot_dim
+                dense = h * (l.q_rank + row) + l.q_rank * l.heads * (l.dim + l.rot_dim) + l.heads * l.vdim * h \
+                    + l.heads * (l.dim * l.kv_rank + l.kv_rank * l.vdim)
+                scan, state, cache = l.heads * ctx * (row + l.kv_rank), 0, ctx * row
+            else:
+                hd, hv = l.heads * l.dim, l.heads * l.vdim
+                dense = h * (2 * hd + hv) + hv * h
+                scan, state, cache = 2 * hd * l.vdim, hd * l.vdim, 0
+            dense += 3 * h * l.ff + 2 * h * mc.side_dim
+            flops += 2.0 * (dense + scan)
+            # a decode step streams the run's weights, every sequence's visible cache rows (tokens of the window, pooled rows
+            # behind it, latent rows), and reads + writes its fp32 state
+            bytes_ += 2.0 * dense + B * (2.0 * cache + 8.0 * state)
+        return flops + 2.0 * h * v, bytes_ + 2.0 * h * v
     qd, kvd = mc.n_q_heads * 128, mc.n_kv_heads * 128
     per_layer = h * (qd + 2 * kvd) + qd * h + 3 * h * mc.ffn
     flops = mc.n_layers * 2.0 * (per_layer + mc.n_q_heads * ctx * 2 * 128) + 2.0 * h * v
@@ -856,7 +882,9 @@ def run_arch_compare(args) -> None:
 
     from vllm_tgis_adapter_b200.engine.revepel import PRESETS as RVP
 
-    PNX = {**PNX, **FLX, **RVP}   # the presets of the layer-list families
+    from vllm_tgis_adapter_b200.engine.sikazen import PRESETS as SKZ
+
+    PNX = {**PNX, **FLX, **RVP, **SKZ}   # the presets of the layer-list families
 
     torch.cuda.set_device(0)
     hbm_gbs, _ = peaks()

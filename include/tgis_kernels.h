@@ -164,6 +164,24 @@ int tgis_k_sigattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_of
 int tgis_k_sigattn(const void* q, const void* k_cache, const void* v_cache, int32_t dt, const int32_t* seqs_host, int32_t n_seqs,
                    const int32_t* block_table_host, int32_t bt_rows, int32_t bt_stride, const float* head_bias, void* out,
                    const tgis_k_sigattn_geom* g);
+
+/* csrc/attention_pooled.cu: softmax attention over a sliding window plus one mean key / value per block of `pool` tokens that
+ * lies wholly behind it.  Pooled rows: pk [pool_blocks][ceil(32 / pool)][kv_heads * dim], pv likewise with vdim. */
+typedef struct tgis_k_poolattn_geom {
+  int32_t heads, kv_heads, dim, vdim, window, pool, rot_dims;
+  float scale;
+  int32_t unit_norm;
+} tgis_k_poolattn_geom;
+/* y fp32 [T, ldy] = [.. q .. k .. v ..] at the given columns (+ bias [q | k | v] or NULL) -> rotated, unit-normed queries and
+ * cache rows at slots[t] */
+int tgis_k_poolattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const float* bias,
+                         const tgis_k_poolattn_geom* g, const float* cos_sin, float eps, const int32_t* positions,
+                         const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T);
+/* the pooled rows of the blocks this step's tokens complete, then the attention of the step's queries; seqs_host: n_seqs x
+ * (q_start, q_len, kv_len, block_row) */
+int tgis_k_poolattn(const void* q, const void* k_cache, const void* v_cache, void* pk, void* pv, int32_t dt,
+                    const int32_t* seqs_host, int32_t n_seqs, const int32_t* block_table_host, int32_t bt_rows,
+                    int32_t bt_stride, void* out, const tgis_k_poolattn_geom* g);
 /* csrc/recurrent.cu delta_scan_kernel (kernels.h DeltaScan); seqs_host as in tgis_k_attention, tok_slot device */
 int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* decay_raw,
                       int32_t ldd, const float* decay_b, const float* A_log, const float* beta_raw, int32_t ldb, float* S,

@@ -71,7 +71,9 @@ def pooled_window_attention(h: torch.Tensor, w: dict, m: dict, eps: float) -> to
     divided by their root mean square per head."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
-    size, P = int(m["mask"]["size"]), int(m["mask"]["pool"])
+    size, P = int(m["mask"]["size"]), int(m["mask"].get("pool", 0))
+    if P <= 0:          # a plain sliding window: no block is ever complete
+        P = T + size + 1
     q = (h @ w["q"].T + w["q.b"]).view(T, H, d)
     k = (h @ w["k"].T + w["k.b"]).view(T, G, d)
     v = (h @ w["v"].T + w["v.b"]).view(T, G, dv)

@@ -23,12 +23,15 @@ class LiveServer:
         from vllm_tgis_adapter_b200.engine.tokenizer import build_synthetic_tokenizer
         from vllm_tgis_adapter_b200.grpc import grpc_server
 
-        if cfg_name.startswith("revepel-"):   # layer-list family (tests/test_zz_revepel_gpu.py): preset sizes, seeded CPU weights, fp32
+        if cfg_name.startswith(("revepel-", "sikazen-")):   # layer-list families (tests/test_zz_revepel_gpu.py, test_zz_sikazen_gpu.py): preset sizes, seeded CPU weights, fp32
             import dataclasses
             import types
 
             from vllm_tgis_adapter_b200.engine.core import cache_block_bytes
-            from vllm_tgis_adapter_b200.engine.revepel import PRESETS, synthetic_weights as revepel_weights
+            if cfg_name.startswith("sikazen-"):
+                from vllm_tgis_adapter_b200.engine.sikazen import PRESETS, synthetic_weights as revepel_weights
+            else:
+                from vllm_tgis_adapter_b200.engine.revepel import PRESETS, synthetic_weights as revepel_weights
 
             mc = dataclasses.replace(PRESETS[cfg_name], max_model_len=256, dtype="float32")
             self.cfg = c = types.SimpleNamespace(vocab=mc.vocab, model_config=mc)

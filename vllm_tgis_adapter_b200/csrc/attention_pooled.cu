@@ -281,6 +281,222 @@ poolattn_kernel(const CT* __restrict__ q, const CT* __restrict__ k_cache, const 
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------- tensor cores
+// bf16 queries and cache rows, dim a multiple of 16 (<= 16 MMA_KS), vdim a multiple of 8 (<= 32 MMA_NT per warp).  Both products
+// on mma.sync m16n8k16 with fp32 accumulators: the tile's 16 queries are the M rows; for the scores each of the four warps owns
+// 8 of a chunk's 32 keys (the query's A fragments stay in registers for the whole walk, key rows are B fragments as they lie;
+// the chunk after the current one lands in a second buffer through cp.async meanwhile), for the weighted sum each warp owns
+// every fourth group of 8 value columns (value rows through ldmatrix.trans).  Scale, mask and the running softmax are fp32 on
+// the accumulator fragments; the weights are rounded to bf16 once and the SAME rounded numbers are summed for the normaliser.
+// Pooled chunks and token chunks differ only in where a row comes from and in which queries see it.
+constexpr int MMA_KS = 8, MMA_NT = 8;
+__device__ __forceinline__ void pa_ldsm_x4(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void pa_ldsm_x2(uint32_t (&r)[2], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void pa_ldsm_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void pa_cp_async16(void* smem, const void* gmem) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void pa_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(PA_THREADS)
+poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                    const __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ pk,
+                    const __nv_bfloat16* __restrict__ pv, const AttnSeq* __restrict__ seqs, const LatentTile* __restrict__ tiles,
+                    const int32_t* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ out, PoolAttnGeom g) {
+  using bf = __nv_bfloat16;
+  extern __shared__ __align__(16) uint8_t pam_smem[];
+  const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8, LDP = KV_BLOCK + 8;
+  bf* Qs = reinterpret_cast<bf*>(pam_smem);            // [16][LDK]
+  bf* Ks2 = Qs + PA_QT * LDK;                          // [2][32][LDK]   two chunks: one in use, the next one landing
+  bf* Vs2 = Ks2 + 2 * KV_BLOCK * LDK;                  // [2][32][LDV]
+  bf* Ps = Vs2 + 2 * KV_BLOCK * LDV;                   // [16][LDP]
+  float* smax = reinterpret_cast<float*>(Ps + PA_QT * LDP);   // [4][16]; reused for the final row sums
+  griddep_launch();
+  griddep_wait();
+  const LatentTile tl = tiles[blockIdx.x];
+  const AttnSeq sq = seqs[tl.seq];
+  const int h = blockIdx.y, kvh = h / (g.heads / g.kv_heads);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t2 = (lane & 3) * 2;
+  const int row0 = sq.q_start + tl.q0, pos0 = sq.kv_len - sq.q_len + tl.q0, nq = tl.nq, pos_last = pos0 + nq - 1;
+  const int dch = d / 8, vch = dv / 8;   // 16-byte chunks per row
+  for (int i = tid; i < PA_QT * dch; i += PA_THREADS) {
+    const int qi = i / dch, ch = i % dch;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (qi < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + qi) * g.heads + h) * d + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + qi * LDK + ch * 8) = v;
+  }
+  __syncthreads();
+  const int nks = d / 16;
+  uint32_t qa[MMA_KS][4];
+#pragma unroll
+  for (int ks = 0; ks < MMA_KS; ++ks)
+    if (ks < nks) pa_ldsm_x4(qa[ks], Qs + (size_t)(lane & 15) * LDK + ks * 16 + (lane >> 4) * 8);
+  float acc[MMA_NT][4];
+#pragma unroll
+  for (int j = 0; j < MMA_NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // rows gq and gq + 8
+  const int n_vis[2] = {pooled_visible(pos0 + gq, g.window, g.pool), pooled_visible(pos0 + gq + 8, g.window, g.pool)};
+  const int n_pooled = pooled_visible(pos_last, g.window, g.pool);
+  const int n_pc = (n_pooled + KV_BLOCK - 1) / KV_BLOCK;
+  const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
+  const int blk0 = kmin / KV_BLOCK, blk1 = pos_last / KV_BLOCK;
+  const int n_chunks = n_pc + blk1 - blk0 + 1;
+  const int rpp = g.rows_per_page();
+  const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
+  // chunk c's K and V rows -> buffer c & 1, as 16-byte asynchronous copies (one commit group per chunk); pooled rows that do
+  // not exist yet are zeros
+  auto fetch = [&](int c) {
+    const bool pooled = c < n_pc;
+    const bf* kb = pooled ? pk : k_cache;
+    const bf* vb = pooled ? pv : v_cache;
+    const size_t page_row = pooled ? 0 : (size_t)bt[blk0 + c - n_pc] * KV_BLOCK;
+    bf* Kd = Ks2 + (size_t)(c & 1) * KV_BLOCK * LDK;
+    bf* Vd = Vs2 + (size_t)(c & 1) * KV_BLOCK * LDV;
+    for (int i = tid; i < KV_BLOCK * (dch + vch); i += PA_THREADS) {
+      const int j = i / (dch + vch), ch = i % (dch + vch);
+      long long r = (long long)page_row + j;
+      if (pooled) {
+        const int b = c * KV_BLOCK + j;
+        r = b < n_pooled ? (long long)pooled_row(b, g.pool, rpp, bt) : -1;
+      }
+      bf* dst = ch < dch ? Kd + j * LDK + ch * 8 : Vd + j * LDV + (ch - dch) * 8;
+      if (r < 0) *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      else if (ch < dch) pa_cp_async16(dst, kb + ((size_t)r * g.kv_heads + kvh) * d + ch * 8);
+      else pa_cp_async16(dst, vb + ((size_t)r * g.kv_heads + kvh) * dv + (ch - dch) * 8);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  fetch(0);
+  for (int c = 0; c < n_chunks; ++c) {
+    const bool pooled = c < n_pc;
+    // the other buffer was last read in the previous pass, which ended with a barrier
+    if (c + 1 < n_chunks) {
+      fetch(c + 1);
+      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    }
+    __syncthreads();   // every thread's copies of chunk c have landed
+    const bf* Ks = Ks2 + (size_t)(c & 1) * KV_BLOCK * LDK;
+    const bf* Vs = Vs2 + (size_t)(c & 1) * KV_BLOCK * LDV;
+    // ---- scores of this warp's 8 keys
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < MMA_KS; ++ks)
+      if (ks < nks) {
+        uint32_t kb2[2];
+        pa_ldsm_x2(kb2, Ks + (size_t)(warp * 8 + (lane & 7)) * LDK + ks * 16 + ((lane >> 3) & 1) * 8);
+        pa_mma(sc, qa[ks], kb2[0], kb2[1]);
+      }
+    bool ok[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int r = e >> 1, qi = gq + r * 8, pi = pos0 + qi;
+      const int kidx = (pooled ? c : blk0 + c - n_pc) * KV_BLOCK + warp * 8 + t2 + (e & 1);   // pooled block number, or token position
+      ok[e] = qi < nq && (pooled ? kidx < n_vis[r] : (kidx <= pi && (g.window <= 0 || pi - kidx < g.window)));
+      sc[e] = ok[e] ? sc[e] * g.scale : -INFINITY;
+    }
+    float mx[2] = {fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])};
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    if ((lane & 3) == 0) {
+      smax[warp * PA_QT + gq] = mx[0];
+      smax[warp * PA_QT + gq + 8] = mx[1];
+    }
+    __syncthreads();
+    float al[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int qi = gq + r * 8;
+      const float bm = fmaxf(fmaxf(smax[qi], smax[PA_QT + qi]), fmaxf(smax[2 * PA_QT + qi], smax[3 * PA_QT + qi]));
+      const float m_new = fmaxf(m_run[r], bm);
+      al[r] = m_new == -INFINITY ? 1.f : expf(m_run[r] - m_new);
+      const bf p0 = __float2bfloat16_rn(ok[2 * r] ? expf(sc[2 * r] - m_new) : 0.f);
+      const bf p1 = __float2bfloat16_rn(ok[2 * r + 1] ? expf(sc[2 * r + 1] - m_new) : 0.f);
+      l_part[r] = fmaf(l_part[r], al[r], __bfloat162float(p0) + __bfloat162float(p1));
+      m_run[r] = m_new;
+      __nv_bfloat162 pp;
+      pp.x = p0; pp.y = p1;
+      *reinterpret_cast<__nv_bfloat162*>(Ps + qi * LDP + warp * 8 + t2) = pp;
+    }
+    __syncthreads();
+    // ---- weighted sum of the values: this warp's groups of 8 columns
+    uint32_t a0[4], a1[4];
+    pa_ldsm_x4(a0, Ps + (size_t)(lane & 15) * LDP + (lane >> 4) * 8);
+    pa_ldsm_x4(a1, Ps + (size_t)(lane & 15) * LDP + 16 + (lane >> 4) * 8);
+#pragma unroll
+    for (int j = 0; j < MMA_NT; ++j) {
+      const int n0 = (warp + 4 * j) * 8;
+      if (n0 < dv) {
+        acc[j][0] *= al[0]; acc[j][1] *= al[0]; acc[j][2] *= al[1]; acc[j][3] *= al[1];
+        uint32_t vb2[4];
+        pa_ldsm_x4_trans(vb2, Vs + (size_t)lane * LDV + n0);
+        pa_mma(acc[j], a0, vb2[0], vb2[1]);
+        pa_mma(acc[j], a1, vb2[2], vb2[3]);
+      }
+    }
+    __syncthreads();   // this pass's buffers, maxima and weights are consumed
+  }
+  // ---- row sums: over the quad, then over the warps
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 1);
+    l_part[r] += __shfl_xor_sync(0xffffffffu, l_part[r], 2);
+  }
+  __syncthreads();
+  if ((lane & 3) == 0) {
+    smax[warp * PA_QT + gq] = l_part[0];
+    smax[warp * PA_QT + gq + 8] = l_part[1];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int qi = gq + r * 8;
+    if (qi >= nq) continue;
+    const float inv_l = 1.f / (smax[qi] + smax[PA_QT + qi] + smax[2 * PA_QT + qi] + smax[3 * PA_QT + qi]);
+    const size_t row = (size_t)(row0 + qi);
+#pragma unroll
+    for (int j = 0; j < MMA_NT; ++j) {
+      const int n = (warp + 4 * j) * 8 + t2;
+      if (n < dv) {
+        __nv_bfloat162 pp;
+        pp.x = __float2bfloat16_rn(acc[j][2 * r] * inv_l); pp.y = __float2bfloat16_rn(acc[j][2 * r + 1] * inv_l);
+        *reinterpret_cast<__nv_bfloat162*>(out + (row * g.heads + h) * dv + n) = pp;
+      }
+    }
+  }
+}
+
+bool mma_eligible(const PoolAttnGeom& g, const void* q, const void* k, const void* v, const void* pk, const void* pv, const void* out) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("TGIS_POOLATTN_MMA");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return on && g.dim % 16 == 0 && g.dim <= 16 * MMA_KS && g.vdim % 8 == 0 && g.vdim <= 32 * MMA_NT && al16(q) && al16(k) && al16(v) &&
+         al16(pk) && al16(pv) && al16(out);
+}
+
 template <class CT>
 cudaError_t launch_fma(const void* q, const void* k_cache, const void* v_cache, const void* pk, const void* pv,
                        const AttnSeq* seqs, const LatentTile* tiles, int n_tiles, const int32_t* block_table, int bt_stride,
@@ -343,6 +559,20 @@ cudaError_t poolattn_launch(const void* q, const void* k_cache, const void* v_ca
                             int bt_stride, void* out, int out_dtype, const PoolAttnGeom& g, cudaStream_t stream) {
   if (n_tiles <= 0) return cudaSuccess;
   if (!geom_ok(g) || out_dtype != dtype) return cudaErrorInvalidValue;
+  if (dtype == DT_BF16 && mma_eligible(g, q, k_cache, v_cache, pk, pv, out)) {
+    using bf = __nv_bfloat16;
+    const size_t smem = ((size_t)(PA_QT + 2 * KV_BLOCK) * (g.dim + 8) + (size_t)2 * KV_BLOCK * (g.vdim + 8) + PA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
+                        4 * PA_QT * sizeof(float);   // <= 77 KB
+    static bool attr_set = false;
+    if (!attr_set) {
+      const cudaError_t e = cudaFuncSetAttribute(poolattn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    return launch_k(poolattn_mma_kernel, dim3(n_tiles, g.heads), dim3(PA_THREADS), smem, stream, reinterpret_cast<const bf*>(q),
+                    reinterpret_cast<const bf*>(k_cache), reinterpret_cast<const bf*>(v_cache), reinterpret_cast<const bf*>(pk),
+                    reinterpret_cast<const bf*>(pv), seqs, tiles, block_table, bt_stride, reinterpret_cast<bf*>(out), g);
+  }
   if (dtype == DT_BF16)
     return launch_fma<__nv_bfloat16>(q, k_cache, v_cache, pk, pv, seqs, tiles, n_tiles, block_table, bt_stride, out, g, stream);
   return launch_fma<float>(q, k_cache, v_cache, pk, pv, seqs, tiles, n_tiles, block_table, bt_stride, out, g, stream);

@@ -673,6 +673,42 @@ int tgis_k_sigattn(const void* q, const void* k_cache, const void* v_cache, int3
   return 0;
 }
 
+static PoolAttnGeom to_pool(const tgis_k_poolattn_geom* g) {
+  return PoolAttnGeom{g->heads, g->kv_heads, g->dim, g->vdim, g->window, g->window > 0 ? g->pool : 0, g->rot_dims, g->scale, g->unit_norm};
+}
+
+int tgis_k_poolattn_prep(const float* y, int32_t ldy, int32_t q_off, int32_t k_off, int32_t v_off, const float* bias,
+                         const tgis_k_poolattn_geom* g, const float* cos_sin, float eps, const int32_t* positions,
+                         const int32_t* slots, void* q_out, void* k_cache, void* v_cache, int32_t dt, int32_t T) {
+  KCK(poolattn_prep_launch(y, ldy, q_off, k_off, v_off, bias, to_pool(g), cos_sin, eps, positions, slots, q_out, k_cache, v_cache,
+                           dt, T, 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
+int tgis_k_poolattn(const void* q, const void* k_cache, const void* v_cache, void* pk, void* pv, int32_t dt,
+                    const int32_t* seqs_host, int32_t n_seqs, const int32_t* block_table_host, int32_t bt_rows,
+                    int32_t bt_stride, void* out, const tgis_k_poolattn_geom* g) {
+  std::vector<AttnSeq> seqs;
+  host_seqs(seqs_host, n_seqs, seqs);
+  std::vector<LatentTile> tiles;
+  int max_q = 0;
+  for (int i = 0; i < n_seqs; ++i) {
+    max_q = std::max(max_q, seqs[i].q_len);
+    for (int q0 = 0; q0 < seqs[i].q_len; q0 += POOLATTN_TILE) tiles.push_back(LatentTile{i, q0, std::min(POOLATTN_TILE, seqs[i].q_len - q0), 0});
+  }
+  Tmp<AttnSeq> d_seqs;
+  Tmp<LatentTile> d_tiles;
+  Tmp<int32_t> d_bt;
+  KCK(d_seqs.upload(seqs.data(), seqs.size()));
+  KCK(d_tiles.upload(tiles.data(), tiles.size()));
+  KCK(d_bt.upload(block_table_host, (size_t)bt_rows * bt_stride));
+  KCK(poolattn_pool_launch(k_cache, v_cache, pk, pv, dt, d_seqs.p, n_seqs, d_bt.p, bt_stride, to_pool(g), max_q, 0));
+  KCK(poolattn_launch(q, k_cache, v_cache, pk, pv, dt, d_seqs.p, d_tiles.p, (int)tiles.size(), d_bt.p, bt_stride, out, dt, to_pool(g), 0));
+  KCK(cudaDeviceSynchronize());
+  return 0;
+}
+
 int tgis_k_delta_scan(const float* q, const float* k, const float* v, int32_t ldq, int32_t ldk, int32_t ldv, const float* decay_raw,
                       int32_t ldd, const float* decay_b, const float* A_log, const float* beta_raw, int32_t ldb, float* S,
                       float* out, int32_t ldo, int32_t heads, int32_t qk_heads, int32_t dim, int32_t vdim,

@@ -76,6 +76,13 @@ class TgisKSigAttnGeom(C.Structure):
     ]
 
 
+class TgisKPoolAttnGeom(C.Structure):
+    _fields_ = [
+        ("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("window", C.c_int32),
+        ("pool", C.c_int32), ("rot_dims", C.c_int32), ("scale", C.c_float), ("unit_norm", C.c_int32),
+    ]
+
+
 class TgisModelSpec(C.Structure):
     _fields_ = [
         ("n_layers", C.c_int32), ("dtype", C.c_int32), ("embed_scale", C.c_float), ("residual_mult", C.c_float),
@@ -136,7 +143,7 @@ ENGINE_SYMBOLS = [
 KERNEL_SYMBOLS = [
     "tgis_k_last_error", "tgis_k_gemm_timeline", "tgis_k_step_timeline_enable", "tgis_k_step_timeline_read", "tgis_k_gemm", "tgis_k_rmsnorm", "tgis_k_opt_layernorm", "tgis_k_opt_bias_act", "tgis_k_opt_embed", "tgis_k_silu_mul", "tgis_k_rope_kv", "tgis_k_gemm_rope", "tgis_k_gemm_norm_chain", "tgis_k_attention",
     "tgis_k_attention_bench", "tgis_k_decode_items", "tgis_k_gemm_plan", "tgis_k_gemm_unit_rows",
-    "tgis_k_sampler", "tgis_k_sampler_ex", "tgis_k_sampler_masked", "tgis_k_lora", "tgis_k_lora_bench", "tgis_k_silu_mul_interleaved", "tgis_k_gemm_any", "tgis_k_rmsnorm_f32", "tgis_k_resid_tail", "tgis_k_latent_prep", "tgis_k_latent_q_rope", "tgis_k_latent_attn", "tgis_k_moe_route", "tgis_k_moe_align", "tgis_k_capattn_prep", "tgis_k_capattn", "tgis_k_sigattn_prep", "tgis_k_sigattn", "tgis_k_delta_scan", "tgis_k_ssd_scan", "tgis_k_token_shift", "tgis_k_short_conv", "tgis_k_selective_scan", "tgis_k_outer_scan", "tgis_k_head_norm_gate", "tgis_k_resid_tail_pair", "tgis_k_sizeof_sample_row", "tgis_k_sizeof_sample_out", "tgis_k_kv_block",
+    "tgis_k_sampler", "tgis_k_sampler_ex", "tgis_k_sampler_masked", "tgis_k_lora", "tgis_k_lora_bench", "tgis_k_silu_mul_interleaved", "tgis_k_gemm_any", "tgis_k_rmsnorm_f32", "tgis_k_resid_tail", "tgis_k_latent_prep", "tgis_k_latent_q_rope", "tgis_k_latent_attn", "tgis_k_moe_route", "tgis_k_moe_align", "tgis_k_capattn_prep", "tgis_k_capattn", "tgis_k_sigattn_prep", "tgis_k_sigattn", "tgis_k_poolattn_prep", "tgis_k_poolattn", "tgis_k_delta_scan", "tgis_k_ssd_scan", "tgis_k_token_shift", "tgis_k_short_conv", "tgis_k_selective_scan", "tgis_k_outer_scan", "tgis_k_head_norm_gate", "tgis_k_resid_tail_pair", "tgis_k_sizeof_sample_row", "tgis_k_sizeof_sample_out", "tgis_k_kv_block",
 ]
 
 _LIB: C.CDLL | None = None
@@ -220,6 +227,9 @@ def load_library() -> C.CDLL:
     sg = C.POINTER(TgisKSigAttnGeom)
     lib.tgis_k_sigattn_prep.argtypes = [vp, i32, i32, i32, i32, sg, vp, vp, vp, vp, vp, vp, i32, i32]
     lib.tgis_k_sigattn.argtypes = [vp, vp, vp, i32, ip, i32, ip, i32, i32, vp, vp, sg]
+    pg = C.POINTER(TgisKPoolAttnGeom)
+    lib.tgis_k_poolattn_prep.argtypes = [vp, i32, i32, i32, i32, vp, pg, vp, f32, vp, vp, vp, vp, vp, i32, i32]
+    lib.tgis_k_poolattn.argtypes = [vp, vp, vp, vp, vp, i32, ip, i32, ip, i32, i32, vp, pg]
     lib.tgis_k_delta_scan.argtypes = [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, i32, vp, vp, i32, i32, i32, i32, i32, ip, i32, vp]
     lib.tgis_k_ssd_scan.argtypes = [vp, vp, vp, i32, i32, i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, ip, i32, vp]
     lib.tgis_k_token_shift.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, i32, i64, i32]
