@@ -62,8 +62,8 @@ __device__ __forceinline__ size_t pooled_row(int b, int pool, int rpp, const int
 
 // ---------------------------------------------------------------------------------------------------------------- prep
 // grid (T, ceil((heads + 2 kv_heads) / 4)), 128 threads: one warp per (token, query head | key head | value head)
-constexpr int PREP_WARPS = 4, PREP_MAX = 16;   // dim <= 32 * PREP_MAX
-template <class CT>
+constexpr int PREP_WARPS = 4, PREP_MAX_DIM = 512;
+template <class CT, int PREP_MAX>   // dim <= 32 * PREP_MAX
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 poolattn_prep_kernel(const float* __restrict__ y, int ldy, int q_off, int k_off, int v_off, const float* __restrict__ bias,
                      PoolAttnGeom g, const float* __restrict__ cos_sin, float eps, const int32_t* __restrict__ positions,
@@ -134,6 +134,7 @@ poolattn_pool_kernel(const CT* __restrict__ k_cache, const CT* __restrict__ v_ca
     const size_t dst = pooled_row(b, P, rpp, bt);
     for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
       float s = 0.f;
+#pragma unroll 4
       for (int r = 0; r < P; ++r) {   // position order
         const int pos = b * P + r;
         const size_t row = (size_t)bt[pos / KV_BLOCK] * KV_BLOCK + pos % KV_BLOCK;
@@ -289,7 +290,7 @@ poolattn_kernel(const CT* __restrict__ q, const CT* __restrict__ k_cache, const 
 // every fourth group of 8 value columns (value rows through ldmatrix.trans).  Scale, mask and the running softmax are fp32 on
 // the accumulator fragments; the weights are rounded to bf16 once and the SAME rounded numbers are summed for the normaliser.
 // Pooled chunks and token chunks differ only in where a row comes from and in which queries see it.
-constexpr int MMA_KS = 8, MMA_NT = 8;
+constexpr int MMA_KS = 8, MMA_NT = 8, PA_NST = 4;
 __device__ __forceinline__ void pa_ldsm_x4(uint32_t (&r)[4], const void* smem) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -323,9 +324,9 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   extern __shared__ __align__(16) uint8_t pam_smem[];
   const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8, LDP = KV_BLOCK + 8;
   bf* Qs = reinterpret_cast<bf*>(pam_smem);            // [16][LDK]
-  bf* Ks2 = Qs + PA_QT * LDK;                          // [2][32][LDK]   two chunks: one in use, the next one landing
-  bf* Vs2 = Ks2 + 2 * KV_BLOCK * LDK;                  // [2][32][LDV]
-  bf* Ps = Vs2 + 2 * KV_BLOCK * LDV;                   // [16][LDP]
+  bf* Ks2 = Qs + PA_QT * LDK;                          // [PA_NST][32][LDK]   a ring of chunks: one in use, the next ones landing
+  bf* Vs2 = Ks2 + PA_NST * KV_BLOCK * LDK;             // [PA_NST][32][LDV]
+  bf* Ps = Vs2 + PA_NST * KV_BLOCK * LDV;              // [16][LDP]
   float* smax = reinterpret_cast<float*>(Ps + PA_QT * LDP);   // [4][16]; reused for the final row sums
   griddep_launch();
   griddep_wait();
@@ -359,42 +360,44 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int n_chunks = n_pc + blk1 - blk0 + 1;
   const int rpp = g.rows_per_page();
   const int32_t* bt = block_table + (size_t)sq.block_row * bt_stride;
-  // chunk c's K and V rows -> buffer c & 1, as 16-byte asynchronous copies (one commit group per chunk); pooled rows that do
-  // not exist yet are zeros
+  // chunk c's K and V rows -> stage c % PA_NST of the ring, as 16-byte asynchronous copies: four threads share a row, every
+  // call is one commit group (an empty one past the last chunk, so that the group count tells which chunk has landed); pooled
+  // rows that do not exist yet are zeros
+  const int fj = tid >> 2, fl = tid & 3;
   auto fetch = [&](int c) {
-    const bool pooled = c < n_pc;
-    const bf* kb = pooled ? pk : k_cache;
-    const bf* vb = pooled ? pv : v_cache;
-    const size_t page_row = pooled ? 0 : (size_t)bt[blk0 + c - n_pc] * KV_BLOCK;
-    bf* Kd = Ks2 + (size_t)(c & 1) * KV_BLOCK * LDK;
-    bf* Vd = Vs2 + (size_t)(c & 1) * KV_BLOCK * LDV;
-    for (int i = tid; i < KV_BLOCK * (dch + vch); i += PA_THREADS) {
-      const int j = i / (dch + vch), ch = i % (dch + vch);
-      long long r = (long long)page_row + j;
+    if (c < n_chunks) {
+      const bool pooled = c < n_pc;
+      long long r;
       if (pooled) {
-        const int b = c * KV_BLOCK + j;
+        const int b = c * KV_BLOCK + fj;
         r = b < n_pooled ? (long long)pooled_row(b, g.pool, rpp, bt) : -1;
+      } else {
+        r = (long long)bt[blk0 + c - n_pc] * KV_BLOCK + fj;
       }
-      bf* dst = ch < dch ? Kd + j * LDK + ch * 8 : Vd + j * LDV + (ch - dch) * 8;
-      if (r < 0) *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-      else if (ch < dch) pa_cp_async16(dst, kb + ((size_t)r * g.kv_heads + kvh) * d + ch * 8);
-      else pa_cp_async16(dst, vb + ((size_t)r * g.kv_heads + kvh) * dv + (ch - dch) * 8);
+      bf* Kd = Ks2 + ((size_t)(c % PA_NST) * KV_BLOCK + fj) * LDK;
+      bf* Vd = Vs2 + ((size_t)(c % PA_NST) * KV_BLOCK + fj) * LDV;
+      if (r < 0) {
+        for (int ch = fl; ch < dch; ch += 4) *reinterpret_cast<uint4*>(Kd + ch * 8) = make_uint4(0, 0, 0, 0);
+        for (int ch = fl; ch < vch; ch += 4) *reinterpret_cast<uint4*>(Vd + ch * 8) = make_uint4(0, 0, 0, 0);
+      } else {
+        const bf* ks = (pooled ? pk : k_cache) + ((size_t)r * g.kv_heads + kvh) * d;
+        const bf* vs = (pooled ? pv : v_cache) + ((size_t)r * g.kv_heads + kvh) * dv;
+        for (int ch = fl; ch < dch; ch += 4) pa_cp_async16(Kd + ch * 8, ks + ch * 8);
+        for (int ch = fl; ch < vch; ch += 4) pa_cp_async16(Vd + ch * 8, vs + ch * 8);
+      }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
-  fetch(0);
+#pragma unroll
+  for (int c = 0; c < PA_NST - 1; ++c) fetch(c);
   for (int c = 0; c < n_chunks; ++c) {
     const bool pooled = c < n_pc;
-    // the other buffer was last read in the previous pass, which ended with a barrier
-    if (c + 1 < n_chunks) {
-      fetch(c + 1);
-      asm volatile("cp.async.wait_group 1;\n" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-    }
+    // the stage that chunk c + PA_NST - 1 goes to was last read in the previous pass, which ended with a barrier
+    fetch(c + PA_NST - 1);
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(PA_NST - 1) : "memory");
     __syncthreads();   // every thread's copies of chunk c have landed
-    const bf* Ks = Ks2 + (size_t)(c & 1) * KV_BLOCK * LDK;
-    const bf* Vs = Vs2 + (size_t)(c & 1) * KV_BLOCK * LDV;
+    const bf* Ks = Ks2 + (size_t)(c % PA_NST) * KV_BLOCK * LDK;
+    const bf* Vs = Vs2 + (size_t)(c % PA_NST) * KV_BLOCK * LDV;
     // ---- scores of this warp's 8 keys
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -518,7 +521,7 @@ cudaError_t launch_fma(const void* q, const void* k_cache, const void* v_cache, 
 
 bool geom_ok(const PoolAttnGeom& g) {
   return g.heads >= 1 && g.kv_heads >= 1 && g.heads % g.kv_heads == 0 && g.heads <= 65535 && g.dim >= 1 && g.vdim >= 1 &&
-         g.dim <= 32 * PREP_MAX && g.vdim <= POOLATTN_MAX_VDIM && g.rot_dims >= 0 && g.rot_dims <= g.dim && (g.rot_dims & 1) == 0;
+         g.dim <= PREP_MAX_DIM && g.vdim <= POOLATTN_MAX_VDIM && g.rot_dims >= 0 && g.rot_dims <= g.dim && (g.rot_dims & 1) == 0;
 }
 
 }  // namespace
@@ -530,13 +533,15 @@ cudaError_t poolattn_prep_launch(const float* y, int ldy, int q_off, int k_off, 
   if (T <= 0) return cudaSuccess;
   if (!geom_ok(g) || (g.rot_dims > 0 && cos_sin == nullptr)) return cudaErrorInvalidValue;
   const dim3 grid(T, (g.heads + 2 * g.kv_heads + PREP_WARPS - 1) / PREP_WARPS);
+  using bf = __nv_bfloat16;
+  const bool small = g.dim <= 128;   // four entries per lane
   if (dtype == DT_BF16)
-    return launch_k(poolattn_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, bias,
-                    g, cos_sin, eps, positions, slot_mapping, reinterpret_cast<__nv_bfloat16*>(q_out),
-                    reinterpret_cast<__nv_bfloat16*>(k_cache), reinterpret_cast<__nv_bfloat16*>(v_cache));
-  return launch_k(poolattn_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, stream, y, ldy, q_off, k_off, v_off, bias, g, cos_sin,
-                  eps, positions, slot_mapping, reinterpret_cast<float*>(q_out), reinterpret_cast<float*>(k_cache),
-                  reinterpret_cast<float*>(v_cache));
+    return launch_k(small ? poolattn_prep_kernel<bf, 4> : poolattn_prep_kernel<bf, PREP_MAX_DIM / 32>, grid, dim3(PREP_WARPS * 32), 0,
+                    stream, y, ldy, q_off, k_off, v_off, bias, g, cos_sin, eps, positions, slot_mapping, reinterpret_cast<bf*>(q_out),
+                    reinterpret_cast<bf*>(k_cache), reinterpret_cast<bf*>(v_cache));
+  return launch_k(small ? poolattn_prep_kernel<float, 4> : poolattn_prep_kernel<float, PREP_MAX_DIM / 32>, grid, dim3(PREP_WARPS * 32),
+                  0, stream, y, ldy, q_off, k_off, v_off, bias, g, cos_sin, eps, positions, slot_mapping,
+                  reinterpret_cast<float*>(q_out), reinterpret_cast<float*>(k_cache), reinterpret_cast<float*>(v_cache));
 }
 
 cudaError_t poolattn_pool_launch(const void* k_cache, const void* v_cache, void* pk, void* pv, int dtype,
@@ -561,11 +566,11 @@ cudaError_t poolattn_launch(const void* q, const void* k_cache, const void* v_ca
   if (!geom_ok(g) || out_dtype != dtype) return cudaErrorInvalidValue;
   if (dtype == DT_BF16 && mma_eligible(g, q, k_cache, v_cache, pk, pv, out)) {
     using bf = __nv_bfloat16;
-    const size_t smem = ((size_t)(PA_QT + 2 * KV_BLOCK) * (g.dim + 8) + (size_t)2 * KV_BLOCK * (g.vdim + 8) + PA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
-                        4 * PA_QT * sizeof(float);   // <= 77 KB
+    const size_t smem = ((size_t)(PA_QT + PA_NST * KV_BLOCK) * (g.dim + 8) + (size_t)PA_NST * KV_BLOCK * (g.vdim + 8) + PA_QT * (KV_BLOCK + 8)) * sizeof(bf) +
+                        4 * PA_QT * sizeof(float);   // <= 108 KB
     static bool attr_set = false;
     if (!attr_set) {
-      const cudaError_t e = cudaFuncSetAttribute(poolattn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024);
+      const cudaError_t e = cudaFuncSetAttribute(poolattn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
       if (e != cudaSuccess) return e;
       attr_set = true;
     }

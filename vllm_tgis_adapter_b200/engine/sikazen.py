@@ -269,13 +269,13 @@ PRESETS: dict[str, ModelConfig] = {
         LayerSpec("latent_attention", heads=4, dim=16, rot_dim=8, vdim=24, kv_rank=40, q_rank=48, scale=0.2, rot_dims=8,
                   rot_base=1000.0)], side_dim=8, loop=(1, 3, 2)),
     "sikazen-1k": _stack(1024, 32768, [
-        _attn(8, 2, 128, 1024, 64, 3072),
+        _attn(8, 2, 128, 256, 16, 3072),
         _latent(8, 128, 64, 256, 512, 3072),
         LayerSpec("hgrn2", heads=8, dim=128, vdim=128, ff=3072),
-        _attn(8, 2, 128, 1024, 64, 3072)], side_dim=128, loop=(0, 2, 2)),
+        _attn(8, 2, 128, 256, 16, 3072)], side_dim=128, loop=(0, 2, 2)),
     "sikazen-2k": _stack(2048, 32768, [
-        _attn(16, 4, 128, 2048, 64, 11264),
+        _attn(16, 4, 128, 256, 16, 11264),
         _latent(16, 128, 64, 512, 1024, 11264),
         LayerSpec("hgrn2", heads=16, dim=128, vdim=128, ff=11264),
-        _attn(16, 4, 128, 2048, 64, 11264)], side_dim=256, loop=(0, 2, 2)),
+        _attn(16, 4, 128, 256, 16, 11264)], side_dim=256, loop=(0, 2, 2)),
 }
