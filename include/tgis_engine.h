@@ -143,7 +143,7 @@ typedef struct tgis_config {
 #define TGIS_MIXER_CHANNEL_DELTA 7   /* short convolutions + delta-rule memory whose key channels decay one by one */
 #define TGIS_MIXER_POOLED_ATTENTION 8 /* grouped-query softmax attention: rotary positions, unit-norm queries and keys, a window
                                        * of tokens and one mean key / value for every block of `pool` tokens behind it */
-#define TGIS_MIXER_HGRN 9            /* outer-product memory whose forget gate (bounded below) also decides what is written */
+#define TGIS_MIXER_HGRN 9            /* outer-product memory that writes with the complement of its forget gate (bounded below per channel) */
 #define TGIS_MLP_NONE 0
 #define TGIS_MLP_MOE 1
 #define TGIS_MLP_DENSE_GELU 2        /* down(gelu_tanh(gate h) * (up h)), width `ff` */

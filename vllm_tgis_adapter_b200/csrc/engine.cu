@@ -294,6 +294,14 @@ struct tgis_engine {
   void *pnx_side = nullptr, *pnx_hB = nullptr;       // side table [vocab, n_layers * side_dim]; norm2's rows (operand type)
   float* pnx_x0 = nullptr;                           // the embedding output, kept for the passes of a loop
   int step_max_q = 0;                                // longest portion of the step
+  // the feed-forward of a parallel pair layer reads the same stream as the mixer: its two products run on a second stream
+  // beside the mixer's kernels (fork after the tail that leaves both normed inputs, join before the tail that adds both
+  // outputs), with a product workspace of their own.  TGIS_PAIR_OVERLAP=0: one stream
+  cudaStream_t stream2 = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  DevBuf<float> gemm_ws2;
+  DevBuf<int> gemm_counters2;
+  bool pair_overlap = true, on_side_stream = false;
   size_t off_ltiles16 = 0;                           // query tiles of POOLATTN_TILE tokens (the latent attention's are smaller)
   int step_n_ltiles16 = 0;
   std::vector<PnxLayer> pnx_layers;
@@ -472,6 +480,10 @@ struct tgis_engine {
                 host_phases[i].post);
     }
     for (void* q : pnx_allocs) cudaFree(q);
+    if (stream2) cudaStreamSynchronize(stream2);
+    if (ev_fork) cudaEventDestroy(ev_fork);
+    if (ev_join) cudaEventDestroy(ev_join);
+    if (stream2) cudaStreamDestroy(stream2);
     if (h_stage) cudaFreeHost(h_stage);
     if (h_samp_out) cudaFreeHost(h_samp_out);
     if (h_allow) cudaFreeHost(h_allow);
@@ -1552,6 +1564,15 @@ struct tgis_engine {
         pnx_expected_tensors += 1;
       }
       pnx_hB = pnx_alloc_dt(T * W, true);
+      if (const char* e = getenv("TGIS_PAIR_OVERLAP")) pair_overlap = atoi(e) != 0;
+      if (pair_overlap) {
+        CK(cudaStreamCreateWithFlags(&stream2, cudaStreamNonBlocking));
+        CK(cudaEventCreateWithFlags(&ev_fork, cudaEventDisableTiming));
+        CK(cudaEventCreateWithFlags(&ev_join, cudaEventDisableTiming));
+        gemm_ws2.alloc(gemm_workspace_bytes(num_sms) / sizeof(float));
+        gemm_counters2.alloc(1 << 16);
+        gemm_counters2.zero();
+      }
     }
     // activations
     pnx_resid = pnx_alloc<float>(T * W);
@@ -1955,7 +1976,8 @@ struct tgis_engine {
       if (make_tmap_bf16_2d(&m, X, (uint64_t)pnx_rows_alloc, (uint64_t)K, (uint64_t)K, BT_VALUES[bi], 64) != 0) return false;
       xit = pnx_xmaps.emplace(xkey, m).first;
     }
-    CK(gemm_bf16_launch(wit->second, xit->second, Y, ldy, T, N, K, gemm_ws.p, gemm_counters.p, num_sms, stream, out_mode));
+    CK(gemm_bf16_launch(wit->second, xit->second, Y, ldy, T, N, K, on_side_stream ? gemm_ws2.p : gemm_ws.p,
+                        on_side_stream ? gemm_counters2.p : gemm_counters.p, num_sms, on_side_stream ? stream2 : stream, out_mode));
     ++n_launches;
     return true;
   }
@@ -1973,7 +1995,7 @@ struct tgis_engine {
     a.x_dtype = x_dt; a.w_dtype = pnx_dt; a.y_dtype = y_dt;
     a.T = T; a.N = N; a.K = K; a.ldx = ldx; a.ldw = K; a.ldy = ldy;
     a.batch = 1; a.mode = mode;
-    CK(gemm_any_launch(a, stream));
+    CK(gemm_any_launch(a, on_side_stream ? stream2 : stream));
     ++n_launches;
   }
 
@@ -2216,6 +2238,21 @@ struct tgis_engine {
     const int32_t* d_bt = ds<int32_t>(off_bt);
     const bool last = ri + 1 == (int)pair_runs.size();
     const PnxLayer* nx = last ? nullptr : &pair_runs[ri + 1];
+    // ---- feed-forward on the second norm's rows -> pnx_yS, beside the mixer
+    const bool has_ff = s.mlp == TGIS_MLP_DENSE_SILU;
+    auto feed_forward = [&]() {
+      pnx_gemm(pnx_hB, A, W, l.w_gu, pnx_actS, A, s.ff, T, 2 * s.ff, W, GEMM_ANY_SWIGLU);
+      pnx_gemm(pnx_actS, A, s.ff, l.w_d, pnx_yS, DT_F32, W, T, W, s.ff);
+    };
+    const bool forked = has_ff && stream2 != nullptr;
+    if (forked) {
+      CK(cudaEventRecord(ev_fork, stream));
+      CK(cudaStreamWaitEvent(stream2, ev_fork, 0));
+      on_side_stream = true;
+      feed_forward();
+      on_side_stream = false;
+      CK(cudaEventRecord(ev_join, stream2));
+    }
     // ---- mixer -> pnx_o [T, width] fp32
     if (s.mixer == TGIS_MIXER_POOLED_ATTENTION) {
       const int H = s.heads, ld = l.in_cols;
@@ -2275,12 +2312,8 @@ struct tgis_engine {
       n_launches += 5;
       pnx_gemm(pnx_oA, A, H * s.vdim, l.w_o, pnx_o, DT_F32, W, T, W, H * s.vdim);
     }
-    // ---- feed-forward on the second norm's rows -> pnx_yS
-    const bool has_ff = s.mlp == TGIS_MLP_DENSE_SILU;
-    if (has_ff) {
-      pnx_gemm(pnx_hB, A, W, l.w_gu, pnx_actS, A, s.ff, T, 2 * s.ff, W, GEMM_ANY_SWIGLU);
-      pnx_gemm(pnx_actS, A, s.ff, l.w_d, pnx_yS, DT_F32, W, T, W, s.ff);
-    }
+    if (forked) CK(cudaStreamWaitEvent(stream, ev_join, 0));
+    else if (has_ff) feed_forward();
     const float* w_a = last ? pnx_final_norm : nx->norm1;
     const float* w_b = (!last && nx->sp.mlp == TGIS_MLP_DENSE_SILU) ? nx->norm2 : nullptr;
     const float* extra = (!last && nx->add_x0) ? pnx_x0 : nullptr;

@@ -330,8 +330,8 @@ struct LatentGeom {
   int rot_dims;      // the first rot_dims of the rot_dim rotated dims turn ("rotate half": i pairs with i + rot_dims / 2)
   float scale;
   int interleaved;   // != 0: the rotated entries pair as (2i, 2i + 1) instead of (i, i + rot_dims / 2)
-  const float* sink; // fp32 [heads] or nullptr: the softmax denominator of head h also holds exp(sink[h]) (no key, no value,
-                     // not scaled, counted once)
+  const float* sink; // fp32 [heads] or nullptr: the softmax denominator of head h also holds exp(sink[h]): a term of the
+                     // normaliser alone -- nothing is summed for it and the score scale does not apply to it
   __host__ __device__ int row() const { return kv_rank + rot_dim; }   // cache row / absorbed query length
 };
 // y [T, ldy] fp32 = the fused down-projection [q latent (q_rank) | kv latent (kv_rank) | k_rot (rot_dim) | gate (heads)]:
@@ -410,8 +410,8 @@ cudaError_t sigattn_launch(const void* q, const void* k_cache, const void* v_cac
 // then (unit_norm != 0) q and k divided by their root mean square over dim; score = scale * q . k.  Query i sees the tokens j
 // with 0 <= i - j < window one by one and, with pool > 0, every block b of `pool` consecutive positions that ends at or
 // before i - window (b * pool + pool - 1 <= i - window) through ONE key and ONE value: the means of the block's cached
-// keys and of its values.  Tokens behind the window whose block is not complete by then are not seen.  Tokens and blocks
-// share one softmax.  window <= 0: every earlier position, no blocks.  Query head h reads key/value head h / (heads / kv_heads).
+// keys and of its values.  Tokens behind the window whose block is not complete by then are not seen.  The softmax runs
+// over window tokens and visible blocks together.  window <= 0: every earlier position, no blocks.  Query head h reads key/value head h / (heads / kv_heads).
 struct PoolAttnGeom {
   int heads, kv_heads, dim, vdim, window, pool;
   int rot_dims;

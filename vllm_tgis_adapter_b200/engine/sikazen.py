@@ -9,7 +9,7 @@ keys / values / state of its own; the embedding output is added to the stream be
                       tokens that lies wholly behind the window
   "latent_attention"  causal attention through low-rank latents (one cached row per token), interleaved rotary pairs, and a
                       learned sink per head in the softmax's denominator
-  "hgrn2"             outer-product memory whose forget gate, bounded below, also decides what is written
+  "hgrn2"             outer-product memory that writes a value with the complement of its forget gate; the gate has a lower bound per channel
 
 This module only reads the configuration: sizes and constants go to the native engine as `tgis_model_spec` /
 `tgis_layer_spec` (include/tgis_engine.h), the arithmetic is csrc/engine.cu `pair_layer`, keys, values and latents live in the
