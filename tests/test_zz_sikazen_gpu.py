@@ -461,6 +461,31 @@ def test_long_decoding_crosses_window_pool_and_page_borders_bf16_stays_close():
         assert _rel(got, ref) < TOL if dtype == "float32" else _bf16_close(got, ref), dtype
 
 
+def test_sink_takes_weight_in_prompts_decoding_and_split_decoding():
+    """Sinks large enough to hold a good part of the softmax's weight even among hundreds of keys: leaving the sink out of a
+    prompt's rows, of a decoded token's row, or of the merge of a long sequence's key splits (bf16, more than 256 keys) changes
+    the output by tens of percent."""
+    from oracle import sikazen_oracle as O
+    from vllm_tgis_adapter_b200.engine.sikazen import synthetic_weights
+
+    cfg = _cfg(width=64, vocab=61, layers=[_lay("latent_attention", _lat(4, 16, 8, 16, 32, 24))], side=0, loop=None)
+    toks = _tokens(400, 61, 8)
+    for dtype in ("float32", "bfloat16"):
+        mc = _model(cfg, dtype)
+        weights = synthetic_weights(mc, 19)
+        weights["l0.mix.sink"] = torch.tensor([6.0, 4.0, -2.0, 7.5]).to(torch.bfloat16)
+        ref = O.forward(cfg, weights, toks)
+        no_sink = O.forward(cfg, {**weights, "l0.mix.sink": torch.full((4,), -1e4).to(torch.bfloat16)}, toks)
+        assert _rel(no_sink.numpy(), ref) > 0.1        # the sinks matter at every length
+        eng = _engine(mc, weights)
+        got = [eng.trace_step([("d", toks[:330], list(range(330)))], [])]
+        for t in range(330, 400):
+            got.append(eng.trace_step([("d", [toks[t]], [0])], ["d"] if t == 399 else []))
+        eng.close()
+        got = np.concatenate(got)
+        assert _rel(got, ref) < TOL if dtype == "float32" else _bf16_close(got, ref), dtype
+
+
 def test_mixed_batches_of_unequal_requests_match_each_alone_and_reuse_pages_and_slots():
     from oracle import sikazen_oracle as O
     from vllm_tgis_adapter_b200.engine.sikazen import synthetic_weights
