@@ -319,7 +319,11 @@ __global__ void __launch_bounds__(PA_THREADS)
 poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const __nv_bfloat16* __restrict__ pk,
                     const __nv_bfloat16* __restrict__ pv, const AttnSeq* __restrict__ seqs, const LatentTile* __restrict__ tiles,
-                    const int32_t* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ out, PoolAttnGeom g) {
+                    const int32_t* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ out, PoolAttnGeom g, int gs) {
+  // gs: query heads per tile.  1: the 16 rows are 16 tokens of head blockIdx.y; grid (tiles, heads).  heads / kv_heads (2, 4, 8 or
+  // 16): the rows are (token, head of key/value head blockIdx.y) pairs, 16 / gs tokens x gs heads, so a chunk's rows are fetched
+  // once for the whole group and a decoded token fills gs rows instead of one; grid (tiles, kv_heads, gs), CTA z takes the
+  // tile's tokens [z * 16 / gs, (z + 1) * 16 / gs) and leaves at once when the tile has none there.
   using bf = __nv_bfloat16;
   extern __shared__ __align__(16) uint8_t pam_smem[];
   const int d = g.dim, dv = g.vdim, LDK = d + 8, LDV = dv + 8, LDP = KV_BLOCK + 8;
@@ -332,15 +336,20 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   griddep_wait();
   const LatentTile tl = tiles[blockIdx.x];
   const AttnSeq sq = seqs[tl.seq];
-  const int h = blockIdx.y, kvh = h / (g.heads / g.kv_heads);
+  const int kvh = gs > 1 ? blockIdx.y : blockIdx.y / (g.heads / g.kv_heads);
+  const int h_base = gs > 1 ? kvh * gs : blockIdx.y;     // head of row r: h_base + r % gs
+  const int tpt = PA_QT / gs;                             // tokens of this CTA's rows; token of row r: r / gs
+  const int tok0 = gs > 1 ? blockIdx.z * tpt : 0;
+  if (tok0 >= tl.nq) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, t2 = (lane & 3) * 2;
-  const int row0 = sq.q_start + tl.q0, pos0 = sq.kv_len - sq.q_len + tl.q0, nq = tl.nq, pos_last = pos0 + nq - 1;
+  const int row0 = sq.q_start + tl.q0 + tok0, pos0 = sq.kv_len - sq.q_len + tl.q0 + tok0, nq = min(tpt, tl.nq - tok0);
+  const int pos_last = pos0 + nq - 1;
   const int dch = d / 8, vch = dv / 8;   // 16-byte chunks per row
   for (int i = tid; i < PA_QT * dch; i += PA_THREADS) {
-    const int qi = i / dch, ch = i % dch;
+    const int r = i / dch, ch = i % dch, tq = r / gs;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (qi < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + qi) * g.heads + h) * d + ch * 8);
-    *reinterpret_cast<uint4*>(Qs + qi * LDK + ch * 8) = v;
+    if (tq < nq) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + tq) * g.heads + h_base + r % gs) * d + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LDK + ch * 8) = v;
   }
   __syncthreads();
   const int nks = d / 16;
@@ -352,7 +361,8 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
   for (int j = 0; j < MMA_NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_part[2] = {0.f, 0.f};   // rows gq and gq + 8
-  const int n_vis[2] = {pooled_visible(pos0 + gq, g.window, g.pool), pooled_visible(pos0 + gq + 8, g.window, g.pool)};
+  const int tqr[2] = {gq / gs, (gq + 8) / gs};   // tokens of this thread's two rows
+  const int n_vis[2] = {pooled_visible(pos0 + tqr[0], g.window, g.pool), pooled_visible(pos0 + tqr[1], g.window, g.pool)};
   const int n_pooled = pooled_visible(pos_last, g.window, g.pool);
   const int n_pc = (n_pooled + KV_BLOCK - 1) / KV_BLOCK;
   const int kmin = g.window > 0 ? max(0, pos0 - g.window + 1) : 0;
@@ -410,9 +420,9 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     bool ok[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int r = e >> 1, qi = gq + r * 8, pi = pos0 + qi;
+      const int r = e >> 1, pi = pos0 + tqr[r];
       const int kidx = (pooled ? c : blk0 + c - n_pc) * KV_BLOCK + warp * 8 + t2 + (e & 1);   // pooled block number, or token position
-      ok[e] = qi < nq && (pooled ? kidx < n_vis[r] : (kidx <= pi && (g.window <= 0 || pi - kidx < g.window)));
+      ok[e] = tqr[r] < nq && (pooled ? kidx < n_vis[r] : (kidx <= pi && (g.window <= 0 || pi - kidx < g.window)));
       sc[e] = ok[e] ? sc[e] * g.scale : -INFINITY;
     }
     float mx[2] = {fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3])};
@@ -474,9 +484,10 @@ poolattn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int qi = gq + r * 8;
-    if (qi >= nq) continue;
+    if (tqr[r] >= nq) continue;
     const float inv_l = 1.f / (smax[qi] + smax[PA_QT + qi] + smax[2 * PA_QT + qi] + smax[3 * PA_QT + qi]);
-    const size_t row = (size_t)(row0 + qi);
+    const size_t row = (size_t)(row0 + tqr[r]);
+    const int h = h_base + qi % gs;
 #pragma unroll
     for (int j = 0; j < MMA_NT; ++j) {
       const int n = (warp + 4 * j) * 8 + t2;
@@ -574,9 +585,17 @@ cudaError_t poolattn_launch(const void* q, const void* k_cache, const void* v_ca
       if (e != cudaSuccess) return e;
       attr_set = true;
     }
-    return launch_k(poolattn_mma_kernel, dim3(n_tiles, g.heads), dim3(PA_THREADS), smem, stream, reinterpret_cast<const bf*>(q),
+    static int group_on = -1;
+    if (group_on < 0) {
+      const char* e = getenv("TGIS_POOLATTN_GROUP");
+      group_on = (e && e[0] == '0') ? 0 : 1;
+    }
+    const int per_kv = g.heads / g.kv_heads;
+    const int gs = (group_on && per_kv >= 2 && per_kv <= PA_QT && PA_QT % per_kv == 0) ? per_kv : 1;
+    const dim3 grid = gs > 1 ? dim3(n_tiles, g.kv_heads, gs) : dim3(n_tiles, g.heads, 1);
+    return launch_k(poolattn_mma_kernel, grid, dim3(PA_THREADS), smem, stream, reinterpret_cast<const bf*>(q),
                     reinterpret_cast<const bf*>(k_cache), reinterpret_cast<const bf*>(v_cache), reinterpret_cast<const bf*>(pk),
-                    reinterpret_cast<const bf*>(pv), seqs, tiles, block_table, bt_stride, reinterpret_cast<bf*>(out), g);
+                    reinterpret_cast<const bf*>(pv), seqs, tiles, block_table, bt_stride, reinterpret_cast<bf*>(out), g, gs);
   }
   if (dtype == DT_BF16)
     return launch_fma<__nv_bfloat16>(q, k_cache, v_cache, pk, pv, seqs, tiles, n_tiles, block_table, bt_stride, out, g, stream);
