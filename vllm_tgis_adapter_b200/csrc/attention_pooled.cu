@@ -132,6 +132,33 @@ poolattn_pool_kernel(const CT* __restrict__ k_cache, const CT* __restrict__ v_ca
   const float inv = 1.f / (float)P;
   for (int b = b_lo + blockIdx.y; b < b_hi; b += gridDim.y) {
     const size_t dst = pooled_row(b, P, rpp, bt);
+    if (sizeof(CT) == 2 && nk % 8 == 0 && nv % 8 == 0) {   // bf16 rows of whole 16-byte groups: eight columns per thread
+      for (int c8 = threadIdx.x; c8 < (nk + nv) / 8; c8 += blockDim.x) {
+        const bool is_k = c8 < nk / 8;
+        const int col = is_k ? c8 * 8 : c8 * 8 - nk;
+        float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int r = 0; r < P; ++r) {   // position order
+          const int pos = b * P + r;
+          const size_t row = (size_t)bt[pos / KV_BLOCK] * KV_BLOCK + pos % KV_BLOCK;
+          const uint4 v = *reinterpret_cast<const uint4*>(is_k ? reinterpret_cast<const __nv_bfloat16*>(k_cache) + row * nk + col
+                                                               : reinterpret_cast<const __nv_bfloat16*>(v_cache) + row * nv + col);
+          const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s8[2 * e] += __bfloat162float(v2[e].x);
+            s8[2 * e + 1] += __bfloat162float(v2[e].y);
+          }
+        }
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(s8[2 * e] * inv, s8[2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(is_k ? reinterpret_cast<__nv_bfloat16*>(pk) + dst * nk + col
+                                       : reinterpret_cast<__nv_bfloat16*>(pv) + dst * nv + col) = o;
+      }
+      continue;
+    }
     for (int c = threadIdx.x; c < nk + nv; c += blockDim.x) {
       float s = 0.f;
 #pragma unroll 4

@@ -32,7 +32,7 @@ class ModelConfig:
     arch: str = "llama"
     # arch "ponenex" (engine/ponenex.py), "falerax" (engine/falerax.py), "revepel" (engine/revepel.py) and "sikazen" (engine/sikazen.py): the layers are described one by one;
     # n_q_heads / n_kv_heads / ffn are unused
-    layers: list | None = None          # list[ponenex.LayerSpec] / list[falerax.LayerSpec] / list[revepel.LayerSpec]
+    layers: list | None = None          # list[ponenex.LayerSpec] / list[falerax.LayerSpec] / list[revepel.LayerSpec] / list[sikazen.LayerSpec]
     embed_scale: float = 1.0
     logit_scale: float = 1.0            # logits = head x * logit_scale
     residual_mult: float = 1.0
